@@ -1,7 +1,8 @@
 """The cache manager: paged keys and values per group of layers, block tables per request, and
 slots of fixed-size per-request state.
 
-What a mixer needs is declared by its class (``KVPagesNeed`` or ``StateNeed``); the manager knows
+What a mixer needs is declared by its class (``KVPagesNeed``, ``StateNeed``, or a tuple of needs for a
+mixer that keeps several things: two state tensors, or pages beside state); the manager knows
 nothing about models.  Schedule entries with the same page shape and the same window form one
 *group* with a page pool, a storage tensor and per-request block tables of its own, so a group
 that keeps every key and a group that keeps only a window can grow and shrink independently.
@@ -112,9 +113,23 @@ class StateSlots:
         self.free.append(slot)
 
 
+def need_keys(entry: int, need):
+    """(key, need) for everything schedule entry ``entry`` keeps: a single need has the entry's index as its key; the
+    members of a tuple of needs have the keys (entry, 0), (entry, 1), ..., and members that are tuples themselves go on
+    in the same way, (entry, 1, 0) and so on.  Storage is looked up by these keys."""
+    if need is None:
+        return
+    if isinstance(need, (tuple, list)):
+        base = entry if isinstance(entry, tuple) else (entry,)
+        for index, member in enumerate(need):
+            yield from need_keys(base + (index,), member)
+    else:
+        yield entry, need
+
+
 class CacheManager:
-    """``needs[i]`` is what schedule entry i keeps for itself: a ``KVPagesNeed``, a ``StateNeed`` or
-    None (nothing, or it reads another entry's cache)."""
+    """``needs[i]`` is what schedule entry i keeps for itself: a ``KVPagesNeed``, a ``StateNeed``, a tuple of such
+    (see ``need_keys``) or None (nothing, or it reads another entry's cache)."""
 
     def __init__(self, needs: Sequence[object], page_size: int, num_pages: int, num_slots: int = 64,
                  prefix_sharing: bool = True, model_identity: str = "model"):
@@ -122,12 +137,10 @@ class CacheManager:
             raise ValueError(f"page_size must be positive: {page_size}")
         self.page_size = page_size
         self.groups: List[CacheGroup] = []
-        self.group_of_entry: Dict[int, Tuple[int, int]] = {}  # entry -> (group index, index inside the group)
-        self.state_entries: Dict[int, StateNeed] = {}
+        self.group_of_entry: Dict[object, Tuple[int, int]] = {}  # entry key -> (group index, index inside the group)
+        self.state_entries: Dict[object, StateNeed] = {}
         by_need: Dict[KVPagesNeed, CacheGroup] = {}
-        for entry, need in enumerate(needs):
-            if need is None:
-                continue
+        for entry, need in ((key, member) for index, whole in enumerate(needs) for key, member in need_keys(index, whole)):
             if isinstance(need, StateNeed):
                 self.state_entries[entry] = need
             elif isinstance(need, KVPagesNeed):

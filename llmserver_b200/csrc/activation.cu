@@ -92,3 +92,70 @@ LLM_EXPORT int llm_silu_mul(const void* gate_up, void* out, int n_rows, int inte
     }
     return llm_check_launch("silu_mul");
 }
+
+// Point-wise steps that stand alone (32-bit arithmetic, one rounding on the store):
+//   kind 0  out = max(x, 0)^2                                the activation of a feed-forward without a gate
+//   kind 1  out = tanh(x), x given in 32-bit                 a low-rank projection's activation, narrowed once
+//   kind 2  out = a * tanh(x / a), 32-bit and in place       capped logits
+//   kind 3  out = a * x + b * y                              two branches' outputs joined
+// Eight elements per thread and turn through 16-byte accesses where count and pointers allow, else one by one.
+enum : int { POINT_RELU_SQUARED = 0, POINT_TANH = 1, POINT_SOFTCAP = 2, POINT_SCALED_SUM = 3 };
+
+template <int KIND>
+__device__ __forceinline__ float pointwise_value(float x, float y, float a, float b) {
+    if (KIND == POINT_RELU_SQUARED) { const float r = fmaxf(x, 0.0f); return r * r; }
+    if (KIND == POINT_TANH) return tanhf(x);
+    if (KIND == POINT_SOFTCAP) return a * tanhf(x / a);
+    return a * x + b * y;
+}
+
+template <typename TI, typename TO, int KIND>
+__global__ void pointwise_kernel(const TI* __restrict__ x, const TI* __restrict__ y, TO* out, size_t count, float a, float b,
+                                 int vectors) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    if (vectors) {
+        for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < count / 8; v += stride) {
+            float xs[8], ys[8], result[8];
+            load8<TI>(x + 8 * v, xs);
+            if (KIND == POINT_SCALED_SUM) load8<TI>(y + 8 * v, ys);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) result[i] = pointwise_value<KIND>(xs[i], KIND == POINT_SCALED_SUM ? ys[i] : 0.0f, a, b);
+            store8<TO>(out + 8 * v, result);
+        }
+        return;
+    }
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < count; e += stride)
+        Num<TO>::store(out + e, pointwise_value<KIND>(Num<TI>::load(x + e), KIND == POINT_SCALED_SUM ? Num<TI>::load(y + e) : 0.0f, a, b));
+}
+
+// `in_dtype` is the type of x and y, `out_dtype` of out (x and out may be the same buffer when the types agree).
+LLM_EXPORT int llm_pointwise(int kind, const void* x, const void* y, void* out, long long count, float a, float b, int in_dtype,
+                             int out_dtype, cudaStream_t stream) {
+    if (count <= 0) return LLM_OK;
+    if (kind < 0 || kind > 3 || (kind == POINT_SCALED_SUM && !y) || (kind == POINT_SOFTCAP && !(a > 0.0f))) {
+        llm_set_error("pointwise: kind %d with these arguments is not defined", kind);
+        return LLM_REFUSED;
+    }
+    const int vectors = count % 8 == 0 && aligned16(x) && aligned16(out) && (!y || aligned16(y));
+    const size_t work = vectors ? (size_t)count / 8 : (size_t)count;
+    size_t blocks = (work + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+#define POINT_LAUNCH(TI, TO)                                                                                              \
+    do {                                                                                                                  \
+        if (kind == POINT_RELU_SQUARED) llm_launch(pointwise_kernel<TI, TO, POINT_RELU_SQUARED>, (unsigned)blocks, 256, 0, stream, (const TI*)x, (const TI*)y, (TO*)out, (size_t)count, a, b, vectors); \
+        else if (kind == POINT_TANH) llm_launch(pointwise_kernel<TI, TO, POINT_TANH>, (unsigned)blocks, 256, 0, stream, (const TI*)x, (const TI*)y, (TO*)out, (size_t)count, a, b, vectors); \
+        else if (kind == POINT_SOFTCAP) llm_launch(pointwise_kernel<TI, TO, POINT_SOFTCAP>, (unsigned)blocks, 256, 0, stream, (const TI*)x, (const TI*)y, (TO*)out, (size_t)count, a, b, vectors); \
+        else llm_launch(pointwise_kernel<TI, TO, POINT_SCALED_SUM>, (unsigned)blocks, 256, 0, stream, (const TI*)x, (const TI*)y, (TO*)out, (size_t)count, a, b, vectors); \
+    } while (0)
+    if (in_dtype == LLM_F32 && out_dtype == LLM_F32) POINT_LAUNCH(float, float);
+    else if (in_dtype == LLM_BF16 && out_dtype == LLM_BF16) POINT_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else if (in_dtype == LLM_F32 && out_dtype == LLM_BF16) POINT_LAUNCH(float, __nv_bfloat16);
+    else {
+        llm_set_error("pointwise: input type %d with output type %d is not supported", in_dtype, out_dtype);
+        return LLM_REFUSED;
+    }
+#undef POINT_LAUNCH
+    return llm_check_launch("pointwise");
+}

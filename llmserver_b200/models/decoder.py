@@ -61,15 +61,22 @@ class DecoderModel:
 
     def bind_cache(self, cache) -> None:
         """Resolves every schedule entry's view of the cache manager's storage."""
+        def view_of(key, need, writes: bool) -> EntryCache:
+            view = EntryCache(writes=writes)
+            if isinstance(need, (tuple, list)):     # a mixer that keeps several things sees one view per member
+                base = key if isinstance(key, tuple) else (key,)
+                view.parts = [view_of(base + (member,), inner, writes) for member, inner in enumerate(need)]
+            if key in cache.group_of_entry:
+                view.k_pages, view.v_pages, view.group = cache.pages_of_entry(key)
+            if key in cache.state_entries:
+                view.state = cache.state_of_entry(key)
+            return view
+
+        needs = self.cache_needs()
         views = []
         for index, entry in enumerate(self.spec.schedule):
             owner = index if entry.cache_from is None else entry.cache_from
-            view = EntryCache(writes=entry.cache_from is None)
-            if owner in cache.group_of_entry:
-                view.k_pages, view.v_pages, view.group = cache.pages_of_entry(owner)
-            if owner in cache.state_entries:
-                view.state = cache.state_of_entry(owner)
-            views.append(view)
+            views.append(view_of(owner, needs[owner], entry.cache_from is None))
         self.entry_caches = views
 
     # ------------------------------------------------------------------ the step
@@ -105,4 +112,7 @@ class DecoderModel:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=residual.device)
         # final norm only where logits are wanted (utils/model.py:147-157)
         normed = self.final_norm.add_norm(residual, delta, rows=batch.logit_rows)
-        return ops.linear(normed, self.head, out_dtype=torch.float32)
+        logits = ops.linear(normed, self.head, out_dtype=torch.float32)
+        if self.spec.logit_softcap:
+            ops.softcap_(logits, self.spec.logit_softcap)
+        return logits

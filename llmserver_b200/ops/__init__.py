@@ -21,7 +21,8 @@ __all__ = ["KernelError", "embedding", "add_rmsnorm", "rmsnorm", "silu_mul", "sa
            "moe_grouped_supported", "moe_combine_rows", "ExpertPlan",
            "clamped_glu", "gemm_f32", "linear", "linear_wide", "qkv_projection", "gate_up_silu", "interleave_gate_up", "require_device", "library", "launch_count",
            "RowScaled", "StreamSink", "STREAM_ROWS", "unscaled_rows_supported", "norm_rope_units", "attention_diff", "gla_supported",
-           "gla_recurrent", "head_linear"]
+           "gla_recurrent", "head_linear", "relu_squared", "tanh_narrow", "softcap_", "scaled_sum", "token_shift_mix",
+           "short_conv_units", "matrix_recurrence_supported", "wkv_recurrent", "delta_rule_recurrent"]
 
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None, scale: float = 1.0) -> torch.Tensor:
@@ -436,6 +437,166 @@ def gla_recurrent(proj: torch.Tensor, q_column: int, k_column: int, v_column: in
 
 GLA_SEGMENT = 64          # fewest tokens per segment of the segmented recurrence
 GLA_MAX_SEGMENTS = 128    # most segments per sequence (the scratch holds a state per segment)
+
+
+def _pointwise(kind: int, x: torch.Tensor, y: Optional[torch.Tensor], out: torch.Tensor, a: float = 0.0, b: float = 0.0) -> torch.Tensor:
+    check(x, "x")
+    check(out, "output")
+    if y is not None:
+        check(y, "y", x.dtype)
+        if y.shape != x.shape:
+            raise KernelError(f"y {tuple(y.shape)} does not match x {tuple(x.shape)}")
+    if out.shape != x.shape:
+        raise KernelError(f"the output {tuple(out.shape)} does not match x {tuple(x.shape)}")
+    call("llm_pointwise", int(kind), x.data_ptr(), pointer(y), out.data_ptr(), x.numel(), float(a), float(b), dtype_code(x.dtype),
+         dtype_code(out.dtype), stream_handle())
+    return out
+
+
+def relu_squared(x: torch.Tensor) -> torch.Tensor:
+    """max(x, 0)^2, formed in 32-bit and rounded once."""
+    return _pointwise(0, x, None, torch.empty_like(x))
+
+
+def tanh_narrow(x: torch.Tensor, act_dtype: torch.dtype) -> torch.Tensor:
+    """tanh of 32-bit values, stored in the activation type."""
+    check(x, "x", torch.float32)
+    return _pointwise(1, x, None, torch.empty(x.shape, dtype=act_dtype, device=x.device))
+
+
+def softcap_(logits: torch.Tensor, cap: float) -> torch.Tensor:
+    """logits <- cap * tanh(logits / cap), in place on 32-bit values."""
+    check(logits, "logits", torch.float32)
+    return _pointwise(2, logits, None, logits, a=cap)
+
+
+def scaled_sum(x: torch.Tensor, a: float, y: torch.Tensor, b: float) -> torch.Tensor:
+    """a * x + b * y in 32-bit, rounded once."""
+    return _pointwise(3, x, y, torch.empty_like(x), a=a, b=b)
+
+
+def token_shift_mix(h: torch.Tensor, shift_state: torch.Tensor, batch, mu: torch.Tensor) -> torch.Tensor:
+    """out[s, n] = h[n] + (h'[n] - h[n]) * mu[s] for the M mixing vectors ``mu`` (float32 [M, width]); h'[n] is the row
+    of the token before in the same sequence, for a sequence's first token of this step the row kept in its slot of
+    ``shift_state`` (float32 [slots, width]; zeros for a new request).  The slot is brought up to date by
+    ``wkv_recurrent``.  Returns [M, N, width] in h's type."""
+    check(h, "h")
+    tokens, width = h.shape
+    check(mu, "mixing vectors", torch.float32, width)
+    check(shift_state, "shift state", torch.float32, width)
+    mixes = mu.shape[0]
+    out = torch.empty((mixes, tokens, width), dtype=h.dtype, device=h.device)
+    call("llm_token_shift_mix", h.data_ptr(), shift_state.data_ptr(), batch.state_slots.data_ptr(), batch.q_start.data_ptr(),
+         batch.seq_of_token.data_ptr(), mu.data_ptr(), out.data_ptr(), tokens, width, mixes, dtype_code(h.dtype), stream_handle())
+    return out
+
+
+def short_conv_units(x: torch.Tensor, column: int, taps_w: torch.Tensor, state: torch.Tensor, batch, n_unit_norm: int,
+                     unit_dim: int, n_scaled: int, n_plain: int, plain_dim: int, norm_eps: float, scale: float) -> torch.Tensor:
+    """A short causal convolution over time, channel by channel, then SiLU:
+
+        y_t[c] = silu(sum_j taps_w[c, j] * x_(t - taps + 1 + j)[c])        zeros before a sequence's start
+
+    over the channels that start at ``column`` of ``x`` [N, row]; ``taps_w`` is float32 [channels, taps], the last column
+    the current token's.  Channels come in units: first ``n_unit_norm`` units of ``unit_dim`` channels, each made a unit
+    vector y / sqrt(sum(y^2) + norm_eps), the first ``n_scaled`` of them multiplied by ``scale``; then ``n_plain`` units of
+    ``plain_dim`` channels that stay as they are.  A sequence's last taps - 1 inputs live in its slot of ``state``
+    (float32 [slots, max(taps - 1, 1), channels]) and are brought up to date.  Returns float32 [N, channels]."""
+    check(x, "x")
+    tokens, row_width = x.shape
+    channels = n_unit_norm * unit_dim + n_plain * plain_dim
+    taps = taps_w.shape[1]
+    check(taps_w, "convolution weights", torch.float32)
+    if taps_w.shape[0] != channels or column < 0 or column + channels > row_width:
+        raise KernelError(f"{channels} channels from column {column} do not fit rows of {row_width} or weights {tuple(taps_w.shape)}")
+    check(state, "convolution state", torch.float32, channels)
+    if state.dim() != 3 or state.shape[1] != max(taps - 1, 1):
+        raise KernelError(f"the convolution state must be [slots, {max(taps - 1, 1)}, {channels}], got {tuple(state.shape)}")
+    out = torch.empty((tokens, channels), dtype=torch.float32, device=x.device)
+    call("llm_short_conv_units", x.data_ptr(), row_width, int(column), taps_w.data_ptr(), int(taps), state.data_ptr(),
+         batch.state_slots.data_ptr(), batch.q_start.data_ptr(), out.data_ptr(), batch.n_seqs, int(n_unit_norm), int(unit_dim),
+         int(n_scaled), int(n_plain), int(plain_dim), float(norm_eps), float(scale), dtype_code(x.dtype), stream_handle())
+    return out
+
+
+def matrix_recurrence_supported(dim: int, value_dim: int) -> bool:
+    return bool(library().llm_matrix_recurrence_supports(int(dim), int(value_dim)))
+
+
+def wkv_recurrent(rkvg: torch.Tensor, z: torch.Tensor, w0: torch.Tensor, bonus: torch.Tensor, weight: torch.Tensor,
+                  state: torch.Tensor, batch, heads: int, dim: int, eps: float, h: Optional[torch.Tensor] = None,
+                  shift_state: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The recurrence with a per-channel decay and a bonus for the current token, sequence by sequence, from and into each
+    sequence's slot of ``state`` (float32 [slots, heads, dim, dim]):
+
+        w = exp(-exp(z + w0));  o = (S + diag(u) k v^T)^T r;  S <- diag(w) S + k v^T
+        out = o / sqrt(mean(o^2) + eps) * weight * silu(g)           per head, over its dim value channels
+
+    ``rkvg`` is [4, N, heads * dim] (r, k, v and the gate's pre-activation) in the activation type, ``z`` float32
+    [N, heads * dim], ``w0`` float32 [heads * dim], ``bonus`` (u) float32 [heads, dim], ``weight`` [heads * dim].  With
+    ``h`` and ``shift_state`` the sequence's last row of ``h`` is left in its slot of ``shift_state`` for the next step's
+    ``token_shift_mix``.  Returns [N, heads * dim] in the activation type; the recurrence itself is 32-bit."""
+    check(rkvg, "r, k, v and gate", last_dim=heads * dim)
+    if rkvg.dim() != 3 or rkvg.shape[0] != 4:
+        raise KernelError(f"r, k, v and the gate come as [4, N, {heads * dim}], got {tuple(rkvg.shape)}")
+    tokens = rkvg.shape[1]
+    plane = tokens * heads * dim
+    if 3 * plane >= 2 ** 31:
+        raise KernelError(f"{tokens} tokens of {heads * dim} channels are more than one launch of wkv_recurrent takes")
+    check(z, "decay projection", torch.float32, heads * dim)
+    check(w0, "decay offset", torch.float32)
+    check(bonus, "bonus", torch.float32, dim)
+    check(weight, "norm weight", last_dim=heads * dim)
+    check(state, "recurrent state", torch.float32, dim)
+    if state.dim() != 4 or tuple(state.shape[1:]) != (heads, dim, dim):
+        raise KernelError(f"the state must be [slots, {heads}, {dim}, {dim}], got {tuple(state.shape)}")
+    width = 0
+    if h is not None:
+        check(h, "h", rkvg.dtype)
+        width = h.shape[1]
+        check(shift_state, "shift state", torch.float32, width)
+    out = torch.empty((tokens, heads * dim), dtype=rkvg.dtype, device=rkvg.device)
+    call("llm_wkv_recurrent", rkvg.data_ptr(), heads * dim, 0, plane, 2 * plane, 3 * plane, z.data_ptr(), w0.data_ptr(),
+         bonus.data_ptr(), weight.data_ptr(), state.data_ptr(), batch.state_slots.data_ptr(), batch.q_start.data_ptr(),
+         out.data_ptr(), batch.n_seqs, int(heads), int(dim), float(eps), pointer(h), pointer(shift_state) if h is not None else 0,
+         int(width), dtype_code(rkvg.dtype), dtype_code(weight.dtype), stream_handle())
+    return out
+
+
+def delta_rule_recurrent(proj: torch.Tensor, g_column: int, pre: torch.Tensor, wide: torch.Tensor, a_log: torch.Tensor,
+                         dt_bias: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, batch, heads: int, qk_heads: int,
+                         dim: int, value_dim: int, eps: float) -> torch.Tensor:
+    """The gated delta rule, sequence by sequence, from and into each sequence's slot of ``state`` (float32
+    [slots, heads, dim, value_dim]):
+
+        g = exp(-exp(A) * softplus(a + dt));  beta = sigmoid(b)
+        S <- g S;  d = beta (v - S^T k);  S <- S + k d^T;  o = S^T q
+        out = o / sqrt(mean(o^2) + eps) * weight * silu(gate)         per head, over value_dim; weight [value_dim]
+
+    ``pre`` is float32 [N, 2 * qk_heads * dim + heads * value_dim] = q | k | v as ``short_conv_units`` leaves them (head h
+    reads q/k head h // (heads / qk_heads)); ``wide`` float32 [N, 2 heads] = b | a; ``a_log`` (A) and ``dt_bias`` float32
+    [heads]; the gate's pre-activation is heads * value_dim columns of ``proj`` from ``g_column``.  Returns
+    [N, heads * value_dim] in the activation type; the recurrence itself is 32-bit."""
+    check(proj, "packed projection")
+    tokens, row_width = proj.shape
+    if g_column < 0 or g_column + heads * value_dim > row_width:
+        raise KernelError(f"the gate's columns {g_column}..{g_column + heads * value_dim} lie outside a row of {row_width}")
+    check(pre, "convolved q, k, v", torch.float32, 2 * qk_heads * dim + heads * value_dim)
+    check(wide, "b and a", torch.float32, 2 * heads)
+    check(a_log, "A", torch.float32)
+    check(dt_bias, "dt bias", torch.float32)
+    check(weight, "norm weight", last_dim=value_dim)
+    check(state, "recurrent state", torch.float32, value_dim)
+    if state.dim() != 4 or tuple(state.shape[1:]) != (heads, dim, value_dim):
+        raise KernelError(f"the state must be [slots, {heads}, {dim}, {value_dim}], got {tuple(state.shape)}")
+    if pre.shape[0] != tokens or wide.shape[0] != tokens:
+        raise KernelError("every input needs one row per token")
+    out = torch.empty((tokens, heads * value_dim), dtype=proj.dtype, device=proj.device)
+    call("llm_delta_rule_recurrent", proj.data_ptr(), row_width, int(g_column), pre.data_ptr(), pre.shape[1], 0, qk_heads * dim,
+         2 * qk_heads * dim, wide.data_ptr(), a_log.data_ptr(), dt_bias.data_ptr(), weight.data_ptr(), state.data_ptr(),
+         batch.state_slots.data_ptr(), batch.q_start.data_ptr(), out.data_ptr(), batch.n_seqs, int(heads), int(qk_heads), int(dim),
+         int(value_dim), float(eps), dtype_code(proj.dtype), dtype_code(weight.dtype), stream_handle())
+    return out
 
 
 def head_linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:

@@ -35,7 +35,8 @@ class GQAttention(Mixer):
     frequencies, how many elements of a head rotate (``rotary_dim``, at most head_dim) and how they pair
     ("halves" or "interleaved").  An encoding that scales the rotated values (``attention_factor`` other than 1) is
     goes through the rotation kernel that takes a magnitude, which has no per-head norm: with ``qk_norm`` it is
-    refused.  The same kernel serves heads whose values have another size than their keys."""
+    refused.  The same kernel serves heads whose values have another size than their keys; with ``qk_norm`` as well,
+    such heads go through the kernel for heads made of units (pairing "halves" only)."""
 
     KNOWN_PARAMS = ("hidden", "heads", "kv_heads", "head_dim", "scale", "qk_norm", "eps", "window", "bias", "softcap",
                     "value_dim", "sinks", "names", "precise_weights")
@@ -90,8 +91,6 @@ class GQAttention(Mixer):
         self.value_dim = int(params.get("value_dim") or self.head_dim)
         # keys and values of different sizes are rotated and cached by the kernel for split sizes
         self.split = self.value_dim != self.head_dim
-        if self.split and params.get("qk_norm"):
-            raise ValueError("gqa_attention: per-head Q/K norms with values of another size than the keys are not supported")
         name = self.names(params)
         self.qkv = torch.cat([weights[name["q"]], weights[name["k"]], weights[name["v"]]], dim=0).contiguous()
         self.out = weights[name["o"]].contiguous()
@@ -123,6 +122,8 @@ class GQAttention(Mixer):
                                  f"values, and the position encoding's attention_factor is {self.magnitude}")
             self.split = True
         self.inv_freq, self.rotary_dim, self.interleaved = inv_freq, rotary_dim, pairing == "interleaved"
+        if self.interleaved and self.split and self.q_norm is not None:
+            raise ValueError("gqa_attention: per-head Q/K norms with values of another size than the keys rotate in halves only")
 
     feeds_stream = True
 
@@ -132,7 +133,15 @@ class GQAttention(Mixer):
 
     def forward(self, x, batch, cache, sink=None):
         tables = batch.block_tables[cache.group]
-        if self.split:
+        if self.split and self.q_norm is not None:
+            # heads with a norm whose values have another size than their keys: the kernel for heads made of units, one
+            # unit per head
+            qkv = ops.linear(x, self.qkv)
+            ops.norm_rope_units(qkv, batch.positions, batch.seq_of_token, tables, cache.k_pages, cache.v_pages, self.heads,
+                                self.kv_heads, 1, self.head_dim, self.head_dim, self.value_dim, batch.error_flag,
+                                q_weight=self.q_norm, k_weight=self.k_norm, eps=self.eps, inv_freq=self.inv_freq,
+                                rotary_dim=self.rotary_dim if self.inv_freq is not None else 0, write_cache=cache.writes)
+        elif self.split:
             qkv = ops.linear(x, self.qkv)
             ops.rope_kv_write_split(qkv, self.inv_freq, self.magnitude, batch.positions, batch.seq_of_token, tables,
                                     cache.k_pages, cache.v_pages, self.heads, self.kv_heads, self.head_dim, self.value_dim,

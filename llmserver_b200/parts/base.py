@@ -68,7 +68,8 @@ class Mixer(Part):
 
     @classmethod
     def cache_need(cls, params: dict):
-        """``KVPagesNeed``, ``StateNeed`` or None: what one execution of this mixer keeps per request."""
+        """``KVPagesNeed``, ``StateNeed``, a tuple of needs (the mixer then finds a cache view per member in
+        ``cache.parts``) or None: what one execution of this mixer keeps per request."""
         return None
 
     def attach(self, position) -> None:
@@ -156,9 +157,11 @@ class EntryCache:
 
     ``k_pages`` / ``v_pages``: [page, kv_head, slot, head_dim] (None for mixers without pages);
     ``group``: which block table of the batch goes with these pages; ``writes``: False when the
-    entry reads the cache another entry wrote; ``state``: [slot, ...] tensor of per-request state."""
+    entry reads the cache another entry wrote; ``state``: [slot, ...] tensor of per-request state; ``parts``: for a
+    mixer whose need is a tuple, one view per member, in the tuple's order."""
     k_pages: Optional[torch.Tensor] = None
     v_pages: Optional[torch.Tensor] = None
     group: int = 0
     writes: bool = True
     state: Optional[torch.Tensor] = None
+    parts: Optional[list] = None

@@ -1,4 +1,4 @@
-"""SwiGLU feed-forward."""
+"""Dense feed-forwards: SwiGLU, a gated layer with clamped values, and a layer without a gate."""
 from __future__ import annotations
 
 import functools
@@ -87,3 +87,32 @@ class ClampedGLU(FeedForward):
 
     def forward(self, x):
         return ops.linear(ops.clamped_glu(ops.linear(x, self.gate_up), self.limit, self.alpha), self.down)
+
+
+@FEED_FORWARDS.register("squared_relu")
+class SquaredReLU(FeedForward):
+    """A feed-forward without a gate: y = W_down (max(W_up x, 0)^2), no biases.  Parameters: ``hidden``, ``intermediate``;
+    ``names``: pairs (role, tensor name behind the prefix) for the roles up and down.  The activation is formed in 32-bit
+    from the product's result and rounded once."""
+
+    KNOWN_PARAMS = ("hidden", "intermediate", "names")
+    NAMES = {"up": "up", "down": "down"}
+
+    @classmethod
+    def names(cls, params) -> dict:
+        return {**cls.NAMES, **dict(params.get("names") or ())}
+
+    @classmethod
+    def declare_weights(cls, params):
+        hidden, intermediate = int(params["hidden"]), int(params["intermediate"])
+        name = cls.names(params)
+        return {name["up"]: WeightDecl((intermediate, hidden)), name["down"]: WeightDecl((hidden, intermediate))}
+
+    def __init__(self, params, weights, runtime):
+        super().__init__(params, weights, runtime)
+        name = self.names(params)
+        self.up = weights[name["up"]].contiguous()
+        self.down = weights[name["down"]].contiguous()
+
+    def forward(self, x):
+        return ops.linear(ops.relu_squared(ops.linear(x, self.up)), self.down)

@@ -7,7 +7,7 @@ from typing import Optional
 import torch
 
 from .. import ops
-from ..weights.declare import NORM, WeightDecl
+from ..weights.declare import NORM, OFFSET, WeightDecl
 from .base import Norm
 from .registry import NORMS
 
@@ -40,18 +40,22 @@ def add_and_read(residual: torch.Tensor, delta, act_dtype: torch.dtype) -> torch
 class RMSNorm(Norm):
     """y = weight * x / sqrt(mean(x^2) + eps) (utils/layers.py:123-138): weight multiplies, it is not
     (1 + weight); no bias.  Parameters: ``width``, ``eps``; ``tensor``: the weight's name behind the part's prefix
-    (default "weight"; "" when the prefix is the whole name).  Fused with the residual add that precedes
+    (default "weight"; "" when the prefix is the whole name); ``one_plus`` (default False): the tensor holds the weight's
+    distance from one, y = (1 + w) * x / rms: the sum is made once, in 32-bit, when the model is built (in bfloat16 it
+    would round the small w away), and the kernels read that 32-bit weight.  Fused with the residual add that precedes
     it, as the reference's add_rms_norm (utils/fused_ops.py:145-155)."""
 
-    KNOWN_PARAMS = ("width", "eps", "tensor")
+    KNOWN_PARAMS = ("width", "eps", "tensor", "one_plus")
 
     @classmethod
     def declare_weights(cls, params):
-        return {params.get("tensor", "weight"): WeightDecl((params["width"],), NORM)}
+        return {params.get("tensor", "weight"): WeightDecl((params["width"],), OFFSET if params.get("one_plus") else NORM)}
 
     def __init__(self, params, weights, runtime):
         super().__init__(params, weights, runtime)
         self.weight = weights[params.get("tensor", "weight")].contiguous()
+        if params.get("one_plus"):
+            self.weight = (self.weight.to(torch.float32) + 1.0).contiguous()
         self.eps = float(params["eps"])
 
     def add_norm(self, residual, delta, rows=None, unscaled=False):

@@ -77,3 +77,47 @@ class StretchedRotaryPosition(PositionEncoding):
         slope = params.get("magnitude_slope")
         self.attention_factor = (0.1 if slope is None else float(slope)) * math.log(factor) + 1.0
         self.inv_freq = torch.tensor(table, dtype=torch.float64).to(torch.float32).to(runtime.device).contiguous()
+
+
+@POSITION_ENCODINGS.register("banded_rotary")
+class BandedRotaryPosition(PositionEncoding):
+    """Rotary frequencies scaled band by band of their wavelength (the long-context scheme of the Llama 3.1 models):
+    with f_i = theta ** (-2i / R) and the wavelength l_i = 2 pi / f_i,
+
+        l_i < original / high:   f_i              pairs that turn fast stay as they are
+        l_i > original / low:    f_i / factor     pairs that turn slowly are slowed down further
+        between:                 (1 - s) f_i / factor + s f_i,   s = (original / l_i - low) / (high - low)
+
+    Parameters: ``head_dim``, ``theta``, ``rotary_dim`` (default head_dim), ``factor``, ``low``, ``high``, ``original``;
+    optional ``pairing``.  The table is made in float64 and held in float32; the angle position * inv_freq is formed in
+    the kernel that rotates Q and K."""
+
+    KNOWN_PARAMS = ("head_dim", "theta", "rotary_dim", "factor", "low", "high", "original", "pairing")
+
+    def __init__(self, params, weights, runtime):
+        import math
+
+        super().__init__(params, weights, runtime)
+        head_dim, theta = int(params["head_dim"]), float(params["theta"])
+        rotary_dim = int(params.get("rotary_dim") or head_dim)
+        if rotary_dim % 2 or not 0 < rotary_dim <= head_dim:
+            raise ValueError(f"rotary encoding needs an even rotary_dim of at most head_dim {head_dim}, got {rotary_dim}")
+        factor, original = float(params["factor"]), float(params["original"])
+        low, high = float(params["low"]), float(params["high"])
+        if factor <= 0 or original <= 0 or not 0 < low < high:
+            raise ValueError(f"banded rotary needs factor > 0, original > 0 and 0 < low < high, got {factor}, {original}, {low}, {high}")
+        table = []
+        for i in range(rotary_dim // 2):
+            plain = theta ** (-2.0 * i / rotary_dim)
+            wavelength = 2.0 * math.pi / plain
+            if wavelength < original / high:
+                table.append(plain)
+            elif wavelength > original / low:
+                table.append(plain / factor)
+            else:
+                ramp = (original / wavelength - low) / (high - low)
+                table.append((1.0 - ramp) * plain / factor + ramp * plain)
+        self.head_dim, self.rotary_dim = head_dim, rotary_dim
+        self.pairing = params.get("pairing") or "halves"
+        self.attention_factor = 1.0
+        self.inv_freq = torch.tensor(table, dtype=torch.float64).to(torch.float32).to(runtime.device).contiguous()

@@ -6,6 +6,7 @@ from typing import Dict, Tuple
 
 MATRIX = "matrix"   # random mode: N(0, 0.02)
 NORM = "norm"       # random mode: 1 + N(0, 0.1)
+OFFSET = "offset"   # a norm weight stored as its distance from one; random mode: N(0, 0.1)
 TABLE = "table"     # integer table (kept as int32)
 WIDE = "wide"       # always held in float32, whatever the compute dtype (routers, per-head scalars); random mode: N(0, 0.02)
 

@@ -14,7 +14,7 @@ from typing import Dict
 
 import torch
 
-from .declare import MATRIX, NORM, TABLE, WIDE, WeightDecl, declared_weights
+from .declare import MATRIX, NORM, OFFSET, TABLE, WIDE, WeightDecl, declared_weights
 
 
 def _tensor_seed(seed: int, name: str) -> int:
@@ -37,6 +37,8 @@ def random_tensor(name: str, declaration: WeightDecl, seed: int, device="cpu") -
     values = torch.randn(declaration.shape, generator=generator, dtype=torch.float32, device=device)
     if declaration.kind == NORM:
         return values.mul_(0.1).add_(1.0)
+    if declaration.kind == OFFSET:
+        return values.mul_(0.1)
     return values.mul_(0.02)
 
 
