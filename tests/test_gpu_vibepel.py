@@ -1,0 +1,543 @@
+"""Vibepel on the GPU against the plain implementation in plain_vibepel.py: each mechanism alone, then whole models
+through the step function, the cache and the scheduler, cut and batched in different ways, in 32-bit and bfloat16."""
+import copy
+import json
+import math
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_vibepel as plain
+import traces
+from helpers import tokens_for
+from vibepel_configs import VIBEPEL
+
+pytestmark = pytest.mark.gpu
+
+DEVICE = "cuda:0"
+DTYPES = ["float32", "bfloat16"]
+NAMES = sorted(VIBEPEL)
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+F64 = torch.float64
+# Largest allowed |engine - plain| as a fraction of the row's largest |plain logit|.  bfloat16: besides the activations
+# between kernels, every sub-layer reads the 32-bit stream itself rounded to 8 significant bits (there is no norm in
+# front that would bring it to unit size first), and the weights here are drawn for peaked attention and long memories.
+ALLOWED = {"float32": 2e-5, "bfloat16": 6e-2}
+
+
+# ------------------------------------------------------------------------------------------------ model folders
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    """Model folders with random weights, redrawn where the generic random mode would hide a fault: Q/K norm weights large
+    enough for peaked attention, decays that keep state for hundreds of tokens in some channels and lose it at once in
+    others, mixing vectors spread over [0, 1], bonuses, convolution taps and step-size biases far from zero."""
+    from safetensors.torch import load_file, save_file
+
+    import llmserver_b200.models  # noqa: F401
+    from llmserver_b200.config import VibepelConfig
+    from llmserver_b200.weights import write_model_folder
+
+    root = tmp_path_factory.mktemp("vibepel")
+    made = {}
+    for name, (raw, seed) in VIBEPEL.items():
+        folder = write_model_folder(VibepelConfig.from_dict(raw), str(root / name), seed, torch.bfloat16)
+        path = os.path.join(folder, "model.safetensors")
+        tensors = load_file(path)
+        generator = torch.Generator().manual_seed(seed)
+        for key in sorted(tensors):
+            shape = tensors[key].shape
+
+            def draw(deviation, mean=0.0):
+                return (torch.randn(shape, generator=generator) * deviation + mean).to(torch.bfloat16)
+            if key.endswith((".q.norm", ".k.norm")):
+                tensors[key] = draw(0.5, 1.5)                       # scores a few units apart: peaked, yet not an argmax
+            elif key.endswith(".conv"):
+                tensors[key] = draw(0.6)
+            elif key.endswith((".w1", ".w2")):
+                tensors[key] = draw(2.0 / math.sqrt(shape[1]))
+            elif key.endswith((".left.q", ".left.k", ".left.v", ".left.o", ".right.q", ".right.k", ".right.v", ".right.g", ".right.o",
+                               ".mix.r", ".mix.k", ".mix.v", ".mix.g", ".mix.o", ".mlp.up", ".mlp.down")):
+                tensors[key] = draw(1.0 / math.sqrt(shape[1]))
+            elif key.endswith((".right.b", ".right.a")):
+                tensors[key] = draw(2.0 / math.sqrt(shape[1]))
+            elif ".mu." in key:
+                tensors[key] = torch.rand(shape, generator=generator).to(torch.bfloat16)
+            elif key.endswith(".w0"):                                # decays from exp(-e^-6) = 0.998 per token down to exp(-e) = 0.07
+                tensors[key] = (torch.linspace(-6.0, 1.0, shape[0]) + torch.randn(shape, generator=generator) * 0.3).to(torch.bfloat16)
+            elif key.endswith(".u"):
+                tensors[key] = draw(0.5)
+            elif key.endswith(".A_log"):
+                tensors[key] = torch.linspace(-4.0, 0.5, shape[0]).to(torch.bfloat16)
+            elif key.endswith(".dt_bias"):
+                tensors[key] = draw(1.0)
+            elif key == "embed":
+                tensors[key] = draw(1.0)
+        save_file(tensors, path)
+        made[name] = folder
+    return made
+
+
+_PLAIN, _LOGITS = {}, {}
+
+
+def plain_model_of(folder):
+    if folder not in _PLAIN:
+        from safetensors.torch import load_file
+        with open(os.path.join(folder, "config.json")) as handle:
+            config = json.load(handle)
+        _PLAIN[folder] = (config, {key: value.to(F64) for key, value in load_file(os.path.join(folder, "model.safetensors")).items()})
+    return _PLAIN[folder]
+
+
+def plain_logits(folder, tokens):
+    key = (folder, tuple(tokens))
+    if key not in _LOGITS:
+        config, weights = plain_model_of(folder)
+        _LOGITS[key] = plain.forward(config, weights, list(tokens)).numpy()
+    return _LOGITS[key]
+
+
+def run_in_process(folder, dtype, records, max_tokens, page_size=16):
+    from llmserver_b200.engine.replay import TraceReplayer
+
+    replayer = TraceReplayer(folder, dtype, max_tokens, page_size)
+    out = {}
+    for record in records:
+        logits = replayer.run_step(record)
+        if logits is not None:
+            out[record["step"]] = logits
+    replayer.cache.check_invariants()
+    assert not replayer.cache.requests, "requests left in the cache after the trace ended"
+    for group in replayer.cache.groups:
+        assert group.pool.num_available == group.pool.num_pages, "pages were lost"
+    return out, replayer
+
+
+def compare(got, records, requests, folder, dtype, what):
+    """32-bit: every row within the allowance.  bfloat16: a row whose head outputs nearly cancel before they are
+    normalised (the first tokens of a recurrent layer, whose state holds one or two keys) amplifies rounding, so up to
+    one row in fifty may exceed the allowance, none by more than twice."""
+    want = traces.expected_rows(records, requests, lambda name: plain_logits(folder, requests[name]))
+    assert set(got) == set(want), f"{what}: steps with logits differ"
+    errors = []
+    for step in sorted(want):
+        assert got[step].shape == want[step].shape and np.isfinite(got[step]).all(), f"{what} step {step}"
+        scale = np.abs(want[step]).max(axis=-1)
+        errors += [(float(e), step, row) for row, e in enumerate(np.abs(got[step] - want[step]).max(axis=-1) / scale)]
+    worst, step, row = max(errors)
+    over = sum(1 for error, _, _ in errors if error > ALLOWED[dtype])
+    hard = ALLOWED[dtype] if dtype == "float32" else 2 * ALLOWED[dtype]
+    assert worst <= hard, f"{what} step {step}: row {row} differs by {worst:.3e} of its largest logit, allowed {hard:.1e}"
+    assert dtype != "float32" or over == 0
+    assert over <= max(1, len(errors) // 50), f"{what}: {over} of {len(errors)} rows differ by more than {ALLOWED[dtype]:.1e}"
+
+
+def _batch(pieces, slots):
+    """A step's batch for kernels that read only the token axis and the state slots: ``pieces`` = (tokens before, tokens now)."""
+    from llmserver_b200.engine.batch import SequenceSlice, build_batch
+    return build_batch([SequenceSlice(f"r{index}", [0] * now, before, [], [[0]], slots[index]) for index, (before, now) in enumerate(pieces)],
+                       1, DEVICE)
+
+
+# ------------------------------------------------------------------------------------------------ mechanisms alone
+@pytest.mark.parametrize("count", [1, 7, 64, 1000, 4099])
+def test_pointwise_kernels(count):
+    from llmserver_b200 import ops
+    generator = torch.Generator().manual_seed(count)
+    x32 = torch.randn((count,), generator=generator) * 3
+    y32 = torch.randn((count,), generator=generator)
+    for dtype, tolerance in ((torch.float32, 1e-6), (torch.bfloat16, 8e-3)):
+        x, y = x32.to(dtype), y32.to(dtype)
+        got = ops.relu_squared(x.to(DEVICE).view(1, count)).cpu().double().view(-1)
+        assert torch.allclose(got, torch.relu(x.double()) ** 2, atol=tolerance, rtol=tolerance)
+        got = ops.scaled_sum(x.to(DEVICE).view(1, count), 0.6, y.to(DEVICE).view(1, count), -1.7).cpu().double().view(-1)
+        assert torch.allclose(got, 0.6 * x.double() - 1.7 * y.double(), atol=tolerance, rtol=tolerance)
+        got = ops.tanh_narrow(x32.to(DEVICE).view(1, count), dtype).cpu()
+        assert got.dtype == dtype and torch.allclose(got.double().view(-1), torch.tanh(x32.double()), atol=tolerance, rtol=tolerance)
+    logits = (x32 * 20).to(DEVICE).view(1, count)
+    ops.softcap_(logits, 30.0)
+    assert torch.allclose(logits.cpu().double().view(-1), 30.0 * torch.tanh(x32.double() * 20 / 30.0), atol=1e-5, rtol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width", [40, 96, 1000])
+def test_norm_weights_stored_around_zero(dtype, width):
+    """y = (1 + w) x / rms with a small w: the sum 1 + w is 32-bit (in bfloat16 it would round w away)."""
+    from llmserver_b200.parts import NORMS, Runtime
+    from llmserver_b200.parts.norm import NormedDelta, add_and_read
+    generator = torch.Generator().manual_seed(width)
+    w = (torch.randn((width,), generator=generator) * 0.01).to(torch.bfloat16)
+    norm = NORMS.get("rmsnorm")({"width": width, "eps": 1e-6, "tensor": "", "one_plus": True}, {"": w.to(dtype).to(DEVICE)},
+                                Runtime(dtype, torch.device(DEVICE)))
+    assert norm.weight.dtype == torch.float32 and torch.equal(norm.weight.cpu(), 1.0 + w.float())
+    stream = torch.randn((5, width), generator=generator)
+    delta = (torch.randn((5, width), generator=generator) * 3).to(dtype)
+    on_device = stream.clone().to(DEVICE)
+    out = add_and_read(on_device, NormedDelta(delta.to(DEVICE), norm), dtype)
+    want = stream.double() + plain.offset_norm(delta.double(), w.double(), 1e-6)
+    assert torch.allclose(on_device.cpu().double(), want, atol=3e-6, rtol=3e-6) and torch.equal(out.cpu(), on_device.cpu().to(dtype))
+    # the final norm of selected rows, with a pending output in front
+    stream2 = stream.clone().to(DEVICE)
+    rows = torch.tensor([4, 1], dtype=torch.int32, device=DEVICE)
+    got = norm.add_norm(stream2, NormedDelta(delta.to(DEVICE), norm), rows=rows)
+    tolerance = 1e-5 if dtype == torch.float32 else 1e-2
+    assert torch.allclose(got.cpu().double(), plain.offset_norm(want[[4, 1]], w.double(), 1e-6), atol=tolerance, rtol=tolerance)
+    assert torch.equal(stream2.cpu(), stream)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_token_shift_mix_reads_the_row_before_from_the_step_or_the_slot(dtype):
+    from llmserver_b200 import ops
+    generator = torch.Generator().manual_seed(9)
+    width, pieces, slots = 72, [(0, 5), (6, 1), (3, 2)], [2, 0, 3]
+    h = torch.randn((8, width), generator=generator).to(dtype)
+    mu = torch.rand((5, width), generator=generator)
+    stored = torch.randn((4, width), generator=generator)
+    stored[2] = 0.0                                    # the first sequence is new: its slot was zeroed
+    got = ops.token_shift_mix(h.to(DEVICE), stored.to(DEVICE), _batch(pieces, slots), mu.to(DEVICE)).cpu().double()
+    before = torch.stack([stored[2], h[0], h[1], h[2], h[3], stored[0], stored[3], h[6]]).double()
+    want = h.double()[None] + (before - h.double())[None] * mu.double()[:, None, :]
+    tolerance = 1e-6 if dtype == torch.float32 else 1e-2
+    assert got.shape == (5, 8, width) and torch.allclose(got, want, atol=tolerance, rtol=tolerance)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("taps,normed,unit,n_scaled,n_plain,plain_dim", [(4, 2, 16, 1, 2, 8), (2, 4, 24, 2, 1, 40), (5, 1, 40, 1, 3, 33),
+                                                                        (3, 2, 128, 1, 2, 128), (1, 2, 8, 1, 1, 8), (4, 0, 8, 0, 2, 72)])
+def test_short_convolution_with_history_in_slots(dtype, taps, normed, unit, n_scaled, n_plain, plain_dim):
+    """Three sequences: one continued from an earlier step by portions shorter than the convolution, one new, one a
+    single token; the stored inputs behind the step are compared too, and nobody's slot stays as it is."""
+    from llmserver_b200 import ops
+    generator = torch.Generator().manual_seed(taps * 100 + unit)
+    channels = normed * unit + n_plain * plain_dim
+    lengths = [(0, 1), (1, 2), (3, 9)], [(0, 17)], [(0, 6), (6, 1)]
+    slots = [2, 0, 3]
+    x = [torch.randn((sum(now for _, now in steps), channels + 7), generator=generator).to(dtype) for steps in lengths]
+    taps_w = (torch.randn((channels, taps), generator=generator) * 0.6).to(torch.bfloat16).float()
+    state = torch.zeros((4, max(taps - 1, 1), channels), dtype=torch.float32, device=DEVICE)
+    state[1] = 7.0
+    got = [[] for _ in lengths]
+    for step in range(3):
+        live = [(s, steps[step]) for s, steps in enumerate(lengths) if step < len(steps)]
+        rows = torch.cat([x[s][before:before + now] for s, (before, now) in live]).to(DEVICE)
+        out = ops.short_conv_units(rows, 5, taps_w.to(DEVICE), state, _batch([piece for _, piece in live], [slots[s] for s, _ in live]),
+                                   normed, unit, n_scaled, n_plain, plain_dim, 1e-6, 0.25).cpu().double()
+        at = 0
+        for s, (_, now) in live:
+            got[s].append(out[at:at + now])
+            at += now
+    for s, steps in enumerate(lengths):
+        values = x[s][:, 5:5 + channels].double()
+        y, history = plain.short_convolution(values, taps_w.double())
+        y = plain.silu(y)
+        units = y[:, :normed * unit].reshape(-1, normed, unit) if normed else None
+        if normed:
+            units = units / torch.sqrt((units * units).sum(dim=-1, keepdim=True) + 1e-6)
+            units[:, :n_scaled] = units[:, :n_scaled] * 0.25
+            y = torch.cat([units.reshape(-1, normed * unit), y[:, normed * unit:]], dim=-1)
+        tolerance = 1e-5 if dtype == torch.float32 else 2e-5      # inputs are rounded, the arithmetic is 32-bit in either path
+        assert torch.allclose(torch.cat(got[s]), y, atol=tolerance, rtol=tolerance), f"sequence {s}"
+        if taps > 1:
+            assert torch.equal(state[slots[s]].cpu().double(), history), f"stored inputs of sequence {s}"
+    assert bool((state[1] == 7.0).all())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,dim", [(2, 24), (5, 8), (1, 72), (3, 64), (2, 32), (1, 128), (2, 40)])
+def test_wkv_recurrence_kernel(dtype, heads, dim):
+    """Three sequences in one step: one continues from a state that an earlier step left (in another slot order), one
+    starts from zero, one is a single token.  Decays run from 'forgets at once' to 'keeps for hundreds of tokens'; the
+    state and the stored row behind the step are compared too."""
+    from llmserver_b200 import ops
+    generator = torch.Generator().manual_seed(dim * 7 + heads)
+    inner, width = heads * dim, 48
+    lengths = [(0, 37), (19, 11), (45, 1)]            # (tokens before this step, tokens of this step)
+    total = [before + now for before, now in lengths]
+    rkvg = [torch.randn((4, count, inner), generator=generator).to(dtype) for count in total]
+    z = [torch.randn((count, inner), generator=generator) for count in total]
+    h = [torch.randn((count, width), generator=generator).to(dtype) for count in total]
+    w0 = torch.linspace(-6.0, 1.0, inner)
+    u = torch.randn((heads, dim), generator=generator) * 0.5
+    weight = (1 + 0.2 * torch.randn((inner,), generator=generator)).to(dtype)
+    eps = 1e-5
+
+    def plain_run(sequence):
+        r, k, v, g = (rkvg[sequence][index].double().view(-1, heads, dim) for index in range(4))
+        w = torch.exp(-torch.exp(z[sequence].double() + w0.double())).view(-1, heads, dim)
+        out = torch.zeros_like(v)
+        S = torch.zeros((heads, dim, dim), dtype=F64)
+        for head in range(heads):
+            out[:, head], S[head] = plain.wkv_scan(r[:, head], k[:, head], v[:, head], w[:, head], u[head].double(), S[head])
+        out = plain.rms_divide(out, eps).reshape(-1, inner) * weight.double() * plain.silu(g.reshape(-1, inner))
+        return out, S
+
+    slots = [2, 0, 3]
+    state = torch.zeros((4, heads, dim, dim), dtype=torch.float32, device=DEVICE)
+    shift = torch.zeros((4, width), dtype=torch.float32, device=DEVICE)
+    state[1], shift[1] = 7.0, 7.0          # nobody's slot: must stay as it is
+    earlier = [(2, lengths[2][0]), (1, lengths[1][0])]      # the step before (sequence 2 first, to change the slot order)
+    batch = _batch([(0, count) for _, count in earlier], [slots[s] for s, _ in earlier])
+    ops.wkv_recurrent(torch.cat([rkvg[s][:, :count] for s, count in earlier], dim=1).contiguous().to(DEVICE),
+                      torch.cat([z[s][:count] for s, count in earlier]).to(DEVICE), w0.to(DEVICE), u.to(DEVICE), weight.to(DEVICE), state,
+                      batch, heads, dim, eps, h=torch.cat([h[s][:count] for s, count in earlier]).to(DEVICE), shift_state=shift)
+    assert torch.equal(shift[slots[1]].cpu(), h[1][lengths[1][0] - 1].float())
+    batch = _batch(lengths, slots)
+    got = ops.wkv_recurrent(torch.cat([rkvg[s][:, before:] for s, (before, _) in enumerate(lengths)], dim=1).contiguous().to(DEVICE),
+                            torch.cat([z[s][before:] for s, (before, _) in enumerate(lengths)]).to(DEVICE), w0.to(DEVICE), u.to(DEVICE),
+                            weight.to(DEVICE), state, batch, heads, dim, eps,
+                            h=torch.cat([h[s][before:] for s, (before, _) in enumerate(lengths)]).to(DEVICE), shift_state=shift).cpu().double()
+    tolerance = 2e-5 if dtype == torch.float32 else 2e-2
+    at = 0
+    for s, (before, now) in enumerate(lengths):
+        want, last = plain_run(s)
+        assert torch.allclose(got[at:at + now], want[before:], atol=tolerance, rtol=tolerance), f"sequence {s}"
+        assert torch.allclose(state[slots[s]].cpu().double(), last, atol=2e-4, rtol=2e-4), f"state of sequence {s}"
+        assert torch.equal(shift[slots[s]].cpu(), h[s][-1].float()), f"stored row of sequence {s}"
+        at += now
+    assert bool((state[1] == 7.0).all()) and bool((shift[1] == 7.0).all())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,qk_heads,dim,vdim", [(2, 1, 24, 40), (5, 5, 8, 16), (1, 1, 72, 33), (4, 2, 64, 128), (3, 1, 128, 64),
+                                                     (2, 2, 128, 128), (6, 3, 16, 8), (2, 1, 40, 100)])
+def test_gated_delta_rule_kernel(dtype, heads, qk_heads, dim, vdim):
+    from llmserver_b200 import ops
+    generator = torch.Generator().manual_seed(dim * 7 + vdim)
+    keys, values = qk_heads * dim, heads * vdim
+    lengths = [(0, 37), (19, 11), (45, 1)]
+    total = [before + now for before, now in lengths]
+    proj = [torch.randn((count, values + 3), generator=generator).to(dtype) for count in total]      # the gate's pre-activation from column 3
+    pre = []
+    for count in total:
+        q = torch.nn.functional.normalize(torch.randn((count, qk_heads, dim), generator=generator), dim=-1) * dim ** -0.5
+        k = torch.nn.functional.normalize(torch.randn((count, qk_heads, dim), generator=generator), dim=-1)
+        v = torch.randn((count, values), generator=generator)
+        pre.append(torch.cat([q.reshape(count, keys), k.reshape(count, keys), v], dim=-1))
+    wide = [torch.randn((count, 2 * heads), generator=generator) * 2 for count in total]
+    a_log = torch.linspace(-4.0, 0.5, heads)
+    dt_bias = torch.randn((heads,), generator=generator)
+    weight = (1 + 0.2 * torch.randn((vdim,), generator=generator)).to(dtype)
+    eps = 1e-5
+
+    def plain_run(sequence):
+        p = pre[sequence].double()
+        q, k = p[:, :keys].view(-1, qk_heads, dim), p[:, keys:2 * keys].view(-1, qk_heads, dim)
+        v = p[:, 2 * keys:].view(-1, heads, vdim)
+        beta = torch.sigmoid(wide[sequence][:, :heads].double())
+        g = torch.exp(-torch.exp(a_log.double()) * torch.nn.functional.softplus(wide[sequence][:, heads:].double() + dt_bias.double()))
+        out = torch.zeros_like(v)
+        S = torch.zeros((heads, dim, vdim), dtype=F64)
+        for head in range(heads):
+            group = head // (heads // qk_heads)
+            out[:, head], S[head] = plain.delta_rule_scan(q[:, group], k[:, group], v[:, head], beta[:, head], g[:, head], S[head])
+        gate = plain.silu(proj[sequence][:, 3:3 + values].double()).view(-1, heads, vdim)
+        return (plain.rms_divide(out, eps) * weight.double() * gate).reshape(-1, values), S
+
+    slots = [2, 0, 3]
+    state = torch.zeros((4, heads, dim, vdim), dtype=torch.float32, device=DEVICE)
+    state[1] = 7.0
+    earlier = [(2, lengths[2][0]), (1, lengths[1][0])]
+    batch = _batch([(0, count) for _, count in earlier], [slots[s] for s, _ in earlier])
+    ops.delta_rule_recurrent(torch.cat([proj[s][:count] for s, count in earlier]).to(DEVICE), 3,
+                             torch.cat([pre[s][:count] for s, count in earlier]).to(DEVICE),
+                             torch.cat([wide[s][:count] for s, count in earlier]).to(DEVICE), a_log.to(DEVICE), dt_bias.to(DEVICE),
+                             weight.to(DEVICE), state, batch, heads, qk_heads, dim, vdim, eps)
+    batch = _batch(lengths, slots)
+    got = ops.delta_rule_recurrent(torch.cat([proj[s][before:] for s, (before, _) in enumerate(lengths)]).to(DEVICE), 3,
+                                   torch.cat([pre[s][before:] for s, (before, _) in enumerate(lengths)]).to(DEVICE),
+                                   torch.cat([wide[s][before:] for s, (before, _) in enumerate(lengths)]).to(DEVICE), a_log.to(DEVICE),
+                                   dt_bias.to(DEVICE), weight.to(DEVICE), state, batch, heads, qk_heads, dim, vdim, eps).cpu().double()
+    tolerance = 2e-5 if dtype == torch.float32 else 2e-2
+    at = 0
+    for s, (before, now) in enumerate(lengths):
+        want, last = plain_run(s)
+        assert torch.allclose(got[at:at + now], want[before:], atol=tolerance, rtol=tolerance), f"sequence {s}"
+        assert torch.allclose(state[slots[s]].cpu().double(), last, atol=2e-5, rtol=2e-4), f"state of sequence {s}"
+        at += now
+    assert bool((state[1] == 7.0).all())
+
+
+# ------------------------------------------------------------------------------------------------ whole models
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_whole_prompt_and_token_by_token(folders, name, dtype):
+    vocab = VIBEPEL[name][0]["vocab"]
+    tokens = tokens_for(vocab, 203, 7)
+    records = traces.whole("r", tokens)
+    got, _ = run_in_process(folders[name], dtype, records, traces.rounded(len(tokens)))
+    compare(got, records, {"r": tokens}, folders[name], dtype, f"{name} whole")
+    records = traces.tail_decoded("r", tokens, 60)      # the windows of these models pass over decoded tokens
+    got, _ = run_in_process(folders[name], dtype, records, traces.rounded(len(tokens)), page_size=8)
+    compare(got, records, {"r": tokens}, folders[name], dtype, f"{name} tail decoded")
+    short = tokens[:30]                                 # and from the very first token on, one by one
+    records = traces.tail_decoded("r", short, 29)
+    got, _ = run_in_process(folders[name], dtype, records, traces.rounded(len(short)), page_size=4)
+    compare(got, records, {"r": short}, folders[name], dtype, f"{name} decoded from the start")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_portions_down_to_two_tokens(folders, name, dtype):
+    vocab = VIBEPEL[name][0]["vocab"]
+    tokens = tokens_for(vocab, 181, 11)
+    records = traces.portions("r", tokens, [7, 2, 5, 3, 2, 16, 33, 2, 64, 1, 17])
+    got, _ = run_in_process(folders[name], dtype, records, traces.rounded(len(tokens)), page_size=8)
+    compare(got, records, {"r": tokens}, folders[name], dtype, f"{name} portions")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_mixed_batches_reuse_pages_and_slots(folders, name, dtype):
+    vocab = VIBEPEL[name][0]["vocab"]
+    lengths = {"r0": 110, "r1": 67, "r2": 40, "r3": 131, "r4": 64, "r5": 18, "r6": 99}
+    requests = {key: tokens_for(vocab, length, 31 + index) for index, (key, length) in enumerate(lengths.items())}
+    records, peak = traces.mixed(requests, seed=5)
+    got, replayer = run_in_process(folders[name], dtype, records, peak)
+    compare(got, records, requests, folders[name], dtype, f"{name} mixed")
+    for group in replayer.cache.groups:
+        if group.window is None:
+            assert group.pool.allocations > group.pool.num_pages, "the trace was meant to reuse pages"
+    # seven requests went through four state slots
+    assert replayer.cache.slots.num_slots == 4 and len(replayer.cache.slots.free) == 4
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(folders, dtype):
+    name = "both_kinds"
+    vocab = VIBEPEL[name][0]["vocab"]
+    tokens = tokens_for(vocab, 330, 3)
+    records = traces.tail_decoded("r", tokens, tail=322)
+    got, _ = run_in_process(folders[name], dtype, records, traces.rounded(len(tokens)))
+    compare(got, records, {"r": tokens}, folders[name], dtype, "long decoding")
+
+
+def test_a_lost_state_or_a_window_one_token_off_would_show(folders):
+    """The plain implementation with the recurrent state dropped at a portion's start, or with windows one token longer or
+    shorter, gives logits far outside the allowance: the models of these tests do not hide such faults."""
+    for name in ("wkv_only", "both_kinds", "parallel_only"):
+        config, weights = plain_model_of(folders[name])
+        tokens = tokens_for(config["vocab"], 90, 13)
+        want = plain_logits(folders[name], tokens)
+        scale = np.abs(want).max(axis=-1)
+        lost = plain.forward(config, weights, tokens, lose_state_at=60).numpy()       # the state of the first 60 tokens is gone
+        assert np.array_equal(lost[:60], want[:60])
+        assert (np.abs(lost[60:] - want[60:]).max(axis=-1) / scale[60:]).max() > 5 * ALLOWED["bfloat16"]
+        if name != "wkv_only":
+            for change in (1, -1):
+                other = copy.deepcopy(config)
+                for layer in other["layers"]:
+                    mask = layer["mixer"].get("left", {}).get("mask") if layer["type"] == "parallel" else None
+                    if mask and mask["size"] + change > 0:
+                        mask["size"] += change
+                off = plain.forward(other, weights, tokens).numpy()
+                assert (np.abs(off - want).max(axis=-1) / scale).max() > 2 * ALLOWED["bfloat16"], f"{name}: windows {change:+d}"
+
+
+def test_float32_logits_do_not_depend_on_the_cut(folders):
+    name = "both_kinds"
+    vocab = VIBEPEL[name][0]["vocab"]
+    tokens = tokens_for(vocab, 120, 19)
+    other = tokens_for(vocab, 75, 20)
+    whole, _ = run_in_process(folders[name], "float32", traces.whole("r", tokens), 128)
+    pieces, _ = run_in_process(folders[name], "float32", traces.portions("r", tokens, [3, 2, 40, 1, 1, 9]), 128, page_size=4)
+    assert np.array_equal(np.concatenate([pieces[step] for step in sorted(pieces)]), whole[0])
+    records, peak = traces.mixed({"r": tokens, "o": other}, seed=2)
+    mixed, _ = run_in_process(folders[name], "float32", records, peak)
+    fed = 0
+    for record in records:
+        row = 0
+        for entry in record["entries"]:
+            for place in entry["want"]:
+                if entry["id"] == "r":
+                    assert np.array_equal(mixed[record["step"]][row], whole[0][fed + place])
+                row += 1
+            if entry["id"] == "r":
+                fed += len(entry["tokens"])
+
+
+def test_bfloat16_rows_do_not_depend_on_their_batch(folders):
+    name = "tensor_core_sizes"
+    vocab = VIBEPEL[name][0]["vocab"]
+    requests = {"r": tokens_for(vocab, 170, 19), "o": tokens_for(vocab, 45, 20), "p": tokens_for(vocab, 90, 21)}
+    alone, _ = run_in_process(folders[name], "bfloat16", traces.whole("r", requests["r"]), 192)
+    records, peak = traces.mixed(requests, seed=4)
+    mixed, _ = run_in_process(folders[name], "bfloat16", records, peak)
+    fed, seen = 0, 0
+    for record in records:
+        row = 0
+        for entry in record["entries"]:
+            for place in entry["want"]:
+                if entry["id"] == "r":
+                    want = alone[0][fed + place]
+                    assert np.abs(mixed[record["step"]][row] - want).max() <= 3e-2 * np.abs(want).max()
+                    seen += 1
+                row += 1
+            if entry["id"] == "r":
+                fed += len(entry["tokens"])
+    assert seen > 20
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_greedy_generation_through_the_engine(folders, name, dtype):
+    """Requests of unequal length through the engine's own scheduler (portions, continuous batching, a pool so small
+    that pages come back and are used again, fewer state slots than requests): every generated token maximises the
+    plain logits of its own prefix."""
+    from llmserver_b200 import Engine
+    vocab = VIBEPEL[name][0]["vocab"]
+    prompts = [tokens_for(vocab, length, 50 + length) for length in (5, 23, 41, 9, 30)]
+    engine = Engine(folders[name], max_new_tokens=10, max_batch_size=3, max_num_batched_tokens=32, prefill_chunk_size=12,
+                    kv_cache_num_blocks=40, kv_cache_block_size=4, ignore_eos=True, dtype=dtype)
+    if name == "tensor_core_sizes":
+        engine.warmup()      # products tuned and decode graphs captured ahead of the first request
+    generated = engine.generate(prompts)
+    assert all(len(tokens) == 10 for tokens in generated)
+    for prompt, tokens in zip(prompts, generated):
+        logits = plain_logits(folders[name], list(prompt) + list(tokens))
+        for index, token in enumerate(tokens):
+            row = logits[len(prompt) - 1 + index]
+            assert row[token] >= row.max() - 2 * ALLOWED[dtype] * np.abs(row).max(), f"token {index} of a prompt of {len(prompt)}"
+    engine.cache.check_invariants()
+    assert engine.cache.available() == engine.cache.capacity()
+
+
+def test_trace_run_program(folders, tmp_path):
+    name, dtype = "both_kinds", "float32"
+    vocab = VIBEPEL[name][0]["vocab"]
+    requests = {"x": tokens_for(vocab, 90, 1), "y": tokens_for(vocab, 33, 2), "z": tokens_for(vocab, 130, 3)}
+    records, peak = traces.mixed(requests, seed=9, max_live=2)
+    out_dir = tmp_path / "out"
+    process = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folders[name],
+                              "--dtype", dtype, "--out", str(out_dir), "--max-tokens", str(peak)],
+                             input="\n".join(json.dumps(record) for record in records) + "\n",
+                             capture_output=True, text=True, timeout=600)
+    assert process.returncode == 0, process.stderr[-2000:]
+    assert [line for line in process.stdout.splitlines() if line.startswith("done ")] == [f"done {r['step']}" for r in records]
+    got = {}
+    for record in records:
+        wanted = sum(len(entry["want"]) for entry in record["entries"])
+        if wanted:
+            got[record["step"]] = np.fromfile(out_dir / f"{record['step']}.f32", dtype="<f4").reshape(wanted, vocab)
+    compare(got, records, requests, folders[name], dtype, f"trace_run {name}")
+
+
+def test_generate_command(folders):
+    """The command line a user generates with: ids in, ids out, the model chosen by its config.json."""
+    name = "both_kinds"
+    vocab = VIBEPEL[name][0]["vocab"]
+    prompts = [tokens_for(vocab, 19, 71), tokens_for(vocab, 3, 72)]
+    command = [sys.executable, "-m", "llmserver_b200.cli.generate", "--model", folders[name], "--dtype", "float32",
+               "--max-new-tokens", "6", "--ignore-eos", "--block-size", "8", "--json"]
+    for prompt in prompts:
+        command += ["--prompt-ids", ",".join(str(token) for token in prompt)]
+    process = subprocess.run(command, capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert process.returncode == 0, process.stderr[-2000:]
+    generated = json.loads(process.stdout.strip().splitlines()[-1])["generated"]
+    for prompt, tokens in zip(prompts, generated):
+        assert len(tokens) == 6
+        logits = plain_logits(folders[name], list(prompt) + list(tokens))
+        assert tokens == [int(logits[len(prompt) - 1 + index].argmax()) for index in range(6)]
