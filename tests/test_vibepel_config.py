@@ -64,7 +64,7 @@ def test_refusals():
 def test_specification_parts_and_constants():
     config, spec = _spec(BOTH_KINDS)
     assert [layer.mixer.kind for layer in spec.layers] == ["wkv_time_mix", "parallel_mixers", "wkv_time_mix", "parallel_mixers", "parallel_mixers"]
-    assert spec.tie_head and spec.logit_softcap == 25.0 and spec.embedding_scale == 0.7
+    assert spec.tie_head and spec.logit_softcap == 25.0 and spec.embedding_scale == 2.5
     assert spec.final_norm.get("one_plus") and all(dict(layer.extra)["mixer_out_norm"].get("one_plus") for layer in spec.layers)
     # equal rotary constants share one position part; scaled and unscaled frequencies do not
     assert len(spec.positions) == 3 and spec.layers[0].position is None

@@ -3,7 +3,8 @@ kinds of layers, layers with and without a feed-forward, grouped and ungrouped h
 value heads smaller and larger than key heads, windows of one token, of a few and longer than any prompt, no window, a
 part of a head rotating, all of it or nothing, frequencies scaled band by band or left alone, convolutions of two to
 five taps, branch scales of one and far from it, decay ranks, capped and uncapped logits, and embedding scales of one,
-below and above it."""
+below and above it (the deepest model's is above: a stream that starts small lets every sub-layer's bfloat16 rounding weigh
+more in what the next ones read)."""
 
 
 def _left(heads, kv_heads, dim, vdim, scale, window, dims, base=10000.0, scaling=None):
@@ -32,7 +33,7 @@ def _dense(ff):
 BANDS = {"factor": 4.0, "low": 1.0, "high": 3.0, "original": 48}
 
 WKV_ONLY = {
-    "architecture": "Vibepel", "vocab": 150, "width": 40, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0}, "logit_softcap": 0.0,
+    "architecture": "Vibepel", "vocab": 150, "width": 40, "norm": {"eps": 1e-5}, "embedding": {"scale": 0.6}, "logit_softcap": 0.0,
     "layers": [_wkv(2, 24, 8, None), _wkv(5, 8, 24, _dense(72)), _wkv(1, 72, 4, None)],
 }
 
@@ -47,7 +48,7 @@ PARALLEL_ONLY = {
 }
 
 BOTH_KINDS = {
-    "architecture": "Vibepel", "vocab": 300, "width": 96, "norm": {"eps": 1e-6}, "embedding": {"scale": 0.7}, "logit_softcap": 25.0,
+    "architecture": "Vibepel", "vocab": 300, "width": 96, "norm": {"eps": 1e-6}, "embedding": {"scale": 2.5}, "logit_softcap": 25.0,
     "layers": [
         _wkv(3, 16, 12, _dense(64)),
         _parallel(_left(4, 2, 16, 16, 0.25, 23, 16, base=1e6, scaling={"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64}),
@@ -60,7 +61,7 @@ BOTH_KINDS = {
 
 # sizes at which the bfloat16 path takes its tensor-core kernels (heads of 64 and 128, widths in 64s)
 TENSOR_CORE_SIZES = {
-    "architecture": "Vibepel", "vocab": 384, "width": 192, "norm": {"eps": 1e-6}, "embedding": {"scale": 4.0}, "logit_softcap": 30.0,
+    "architecture": "Vibepel", "vocab": 384, "width": 192, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "logit_softcap": 30.0,
     "layers": [
         _parallel(_left(4, 2, 64, 64, 0.125, 70, 32, base=1e5, scaling={"factor": 8.0, "low": 1.0, "high": 4.0, "original": 128}),
                   _right(4, 2, 64, 64, 4), 0.7, 0.4, _dense(256)),
