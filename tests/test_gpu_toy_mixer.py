@@ -424,8 +424,15 @@ def test_parts_refuse_what_they_cannot_do():
     scaled = attention(good, weights, runtime)
     scaled.attach(rotary(dict(head_dim=16, theta=1e4, attention_factor=1.2), {}, runtime))
     assert scaled.magnitude == 1.2 and scaled.split
+    # per-head norms with values of another size than the keys go through the kernel for heads made of units, which
+    # rotates in halves only
+    normed_weights = {**weights, "v_proj.weight": torch.zeros(8, 32, device=DEVICE), "o_proj.weight": torch.zeros(32, 16, device=DEVICE),
+                      "q_norm.weight": torch.ones(16, device=DEVICE), "k_norm.weight": torch.ones(16, device=DEVICE)}
+    uneven = attention({**good, "qk_norm": True, "value_dim": 8}, normed_weights, runtime)
+    uneven.attach(rotary(dict(head_dim=16, theta=1e4, rotary_dim=8), {}, runtime))
+    assert uneven.split and uneven.rotary_dim == 8
     with pytest.raises(ValueError):
-        attention({**good, "qk_norm": True, "value_dim": 8}, weights, runtime)       # nor with values of another size
+        uneven.attach(rotary(dict(head_dim=16, theta=1e4, pairing="interleaved"), {}, runtime))
     with pytest.raises(ValueError):
         mixer.attach(rotary(dict(head_dim=32, theta=1e4), {}, runtime))            # rotates more than a head holds
     with pytest.raises(ValueError):
