@@ -206,6 +206,59 @@ def dikusun_comparison(args) -> int:
     return 0
 
 
+def vibepel_comparison(args) -> int:
+    """Vibepel beside the Dikusun model of equal size (differential attention over the same window for a parallel layer,
+    gated linear attention for time mixing) and beside the Qwen3 decoder of equal width, heads and feed-forward width: a
+    2048-token prompt in one step and decode steps at batch 1, 8 and 64 (contexts averaging 3072), device-timed like the
+    headline run; bytes and FLOPs counted per step, fractions of the measured peaks.  Random bfloat16 weights."""
+    from llmserver_b200.cli.harness import (VIBEPEL_SIZES, dikusun_dense_cost, dikusun_dense_twin, dikusun_step_cost,
+                                            vibepel_config, vibepel_dikusun_twin, vibepel_step_cost)
+    import llmserver_b200.models  # noqa: F401
+
+    os.environ["PATH"] = os.path.dirname(sys.executable) + os.pathsep + os.environ.get("PATH", "")
+    layers = args.layers if "--layers" in " ".join(sys.argv) else 4
+    peaks, peak_source = read_peaks()
+    wanted = args.sizes.split(",") if args.sizes else list(VIBEPEL_SIZES)
+    steps, warmup = min(args.steps, 32), max(3, min(args.warmup, 4))
+    results, dense_done = {}, {}
+    with ClockSampler() as clocks:
+        for name in wanted:
+            size = VIBEPEL_SIZES[name]
+            results[name] = {"kinds": list(size["kinds"])}
+            twin, twin_config = vibepel_dikusun_twin(size, layers)
+            arms = [("vibepel", size, vibepel_config(size, layers), vibepel_step_cost), ("dikusun", twin, twin_config, dikusun_step_cost)]
+            if size["width"] not in dense_done:
+                arms.append(("dense", twin, dikusun_dense_twin(twin, layers), dikusun_dense_cost))
+            for label, sizes, config, cost in arms:
+                harness = Harness(layers, 64, config=config)
+                row = {}
+                prefill_ms = harness.time_prefill(PROMPT)
+                _, flops = cost(sizes, layers, PROMPT, 1, 0)
+                row["prefill"] = {"ms": round(prefill_ms, 3), "tokens_per_s": round(PROMPT / prefill_ms * 1e3),
+                                  "tflops": round(flops / prefill_ms / 1e9, 1),
+                                  "frac_of_bf16_burst": round(flops / prefill_ms / 1e9 / peaks["bf16_tflops"], 3)}
+                for batch in (1, 8, 64):
+                    harness.time_decode(batch, 4, 3)
+                    run = harness.time_decode(batch, steps, warmup)
+                    bytes_, _ = cost(sizes, layers, batch, batch, run["mean_context"])
+                    gbs = bytes_ / run["ms_per_step"] / 1e6
+                    row[f"decode_b{batch}"] = {"ms": round(run["ms_per_step"], 4), "tokens_per_s": round(run["tokens_per_s"], 1),
+                                               "gb_per_step": round(bytes_ / 1e9, 3), "gbs": round(gbs, 1),
+                                               "frac_of_copy": round(gbs / peaks["hbm_gbs"], 3),
+                                               "graph_steps": harness.step_function.graph_steps}
+                if label == "dense":
+                    dense_done[size["width"]] = row
+                else:
+                    results[name][label] = row
+                harness.close()
+            results[name]["dense"] = dense_done[size["width"]]
+    print(json.dumps({"design": "vibepel", "beside": "Dikusun of equal size (attention for parallel, gla for wkv); Qwen3 dense of equal width, heads and feed-forward width",
+                      "layers": layers, "prompt": PROMPT, "decode_context_mean": MEAN_DECODE_CONTEXT, "dtype": "bf16",
+                      "data": "synthetic: seeded random weights, uniform random token ids", "peaks": {**peaks, "source": peak_source},
+                      "clocks": clocks.summary(), "sizes": results}))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--gpus", type=int, default=1)
@@ -216,7 +269,7 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--skip-points", action="store_true", help="skip the batch-1 and batch-64 points")
-    parser.add_argument("--design", default=None, choices=["gefarax", "dikusun"],
+    parser.add_argument("--design", default=None, choices=["gefarax", "dikusun", "vibepel"],
                         help="instead of the headline run: prefill and decode of this design at a few layer sizes, beside the "
                              "dense decoder of equal size (one JSON line; --layers defaults to 4 here)")
     parser.add_argument("--sizes", default=None, help="with --design: comma-separated names of the sizes to run (default: all)")
@@ -225,6 +278,8 @@ def main() -> int:
         return design_comparison(args)
     if args.design == "dikusun":
         return dikusun_comparison(args)
+    if args.design == "vibepel":
+        return vibepel_comparison(args)
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":

@@ -443,3 +443,77 @@ def dikusun_dense_cost(size: dict, layers: int, tokens: int, sequences: int, con
     pairs = sequences * (per_sequence * context + per_sequence * (per_sequence + 1) / 2)
     return (2.0 * layers * weights + 2.0 * layers * kv * 2 * dim * sequences * (context + per_sequence) + COMPARE_VOCAB * width * 2.0,
             2.0 * tokens * layers * weights + 2.0 * layers * heads * 2 * dim * pairs)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Vibepel beside Dikusun (the closest design: the same block, windowed attention, a recurrence with a matrix state) and
+# beside the dense decoder, at equal size
+# ---------------------------------------------------------------------------------------------------------------------
+def _vibepel_mixers(width, heads, kv_heads):
+    """Mixers of one width: attention with heads of 128 over a window of 1024 tokens, half of each head rotating, beside a
+    gated delta rule with half as many heads of 128 x 128; time mixing with heads of 64 channels across the stream."""
+    left = dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, scale=128 ** -0.5, mask={"size": 1024},
+                rot={"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}})
+    right = dict(heads=heads // 2, kv_heads=kv_heads, dim=128, vdim=128, conv=4)
+    return (dict(left=left, right=right, left_scale=0.6, right_scale=0.5), dict(heads=width // 64, dim=64, w_rank=64))
+
+
+# Layer sizes that resemble served models: four layers of one kind of mixer, or parallel, time mixing, parallel,
+# parallel; every layer has a feed-forward three times as wide as the stream.
+VIBEPEL_SIZES = {}
+for _width, _heads, _kv in ((2048, 16, 4), (4096, 32, 8)):
+    _p, _w = _vibepel_mixers(_width, _heads, _kv)
+    for _label, _kinds in (("parallel", ("parallel",) * 4), ("wkv", ("wkv",) * 4), ("mixed", ("parallel", "wkv", "parallel", "parallel"))):
+        VIBEPEL_SIZES[f"w{_width}-{_label}"] = dict(width=_width, ff=3 * _width, parallel=_p, wkv=_w, kinds=_kinds)
+
+
+def vibepel_config(size: dict, layers: int = None):
+    from llmserver_b200.config import VibepelConfig
+    kinds = size["kinds"] if layers is None else [size["kinds"][index % len(size["kinds"])] for index in range(layers)]
+    return VibepelConfig.from_dict({"architecture": "Vibepel", "vocab": COMPARE_VOCAB, "width": size["width"], "norm": {"eps": 1e-6},
+                                    "embedding": {"scale": 8.0}, "logit_softcap": 30.0,
+                                    "layers": [{"type": kind, "mixer": size[kind], "mlp": {"kind": "dense", "ff": size["ff"]}}
+                                               for kind in kinds]})
+
+
+def vibepel_dikusun_twin(size: dict, layers: int):
+    """The Dikusun model of equal size: differential attention over the same window where Vibepel has a parallel layer,
+    gated linear attention where it has time mixing, the same width and feed-forward width."""
+    attention, _, gla = _dikusun_mixers(size["width"], size["parallel"]["left"]["heads"], size["parallel"]["left"]["kv_heads"])
+    kinds = tuple("attention" if kind == "parallel" else "gla" for kind in size["kinds"])
+    twin = _dikusun_size(size["width"], size["ff"], attention, None, gla, kinds)
+    return twin, dikusun_config(twin, layers)
+
+
+def vibepel_step_cost(size: dict, layers: int, tokens: int, sequences: int, context: float):
+    """(bytes, FLOPs) of one step in which each of ``sequences`` requests brings tokens / sequences new tokens behind
+    ``context`` cached ones: bytes = every weight once + what the mixers read of cache and state (states are read and
+    written); FLOPs = the products of the tokens + attention per (query, key) pair + the recurrences' multiply-adds."""
+    width, ff = size["width"], size["ff"]
+    per_sequence = tokens / sequences
+    total_bytes = COMPARE_VOCAB * width * 2.0
+    flops = 0.0
+    kinds = [size["kinds"][index % len(size["kinds"])] for index in range(layers)]
+    for kind in kinds:
+        weights = 2.0 * width * ff
+        if kind == "parallel":
+            left, right = size["parallel"]["left"], size["parallel"]["right"]
+            heads, kv, dim, vdim, window = left["heads"], left["kv_heads"], left["dim"], left["vdim"], left["mask"]["size"]
+            weights += (heads * dim + kv * dim + kv * vdim) * width + width * heads * vdim
+            seen = min(context + per_sequence, window)
+            total_bytes += sequences * seen * kv * (dim + vdim) * 2.0
+            pairs = sequences * sum(min(context + i + 1, window) for i in range(int(per_sequence)))
+            flops += 2.0 * heads * (dim + vdim) * pairs
+            r_heads, r_kv, r_dim, r_vdim = right["heads"], right["kv_heads"], right["dim"], right["vdim"]
+            weights += (2 * r_kv * r_dim + 2 * r_heads * r_vdim + 2 * r_heads) * width + width * r_heads * r_vdim
+            total_bytes += sequences * r_heads * r_dim * r_vdim * 4.0 * 2
+            flops += tokens * r_heads * r_dim * r_vdim * 8.0          # four multiply-adds per cell of the state
+        else:
+            m = size["wkv"]
+            heads, dim, rank = m["heads"], m["dim"], m["w_rank"]
+            weights += 5 * heads * dim * width + rank * width + heads * dim * rank
+            total_bytes += sequences * heads * dim * dim * 4.0 * 2
+            flops += tokens * heads * dim * dim * 6.0                 # three multiply-adds per cell of the state
+        total_bytes += 2.0 * weights
+        flops += 2.0 * tokens * weights
+    return total_bytes, flops
