@@ -8,7 +8,9 @@
 // (2) Short convolution (`llm_short_conv_units`): y_t[c] = silu(sum_j w[c][j] * x_(t - taps + 1 + j)[c]), zeros before the
 //     sequence's start, the last taps - 1 inputs of every sequence carried in its state slot; channels come in units (a
 //     head's query, key or value channels); the first `n_unit_norm` units are then made unit vectors,
-//     y / sqrt(sum(y^2) + norm_eps), and the first `n_scaled` of those multiplied by `scale`.  Results are 32-bit.
+//     y / sqrt(sum(y^2) + norm_eps), and the first `n_scaled` of those multiplied by `scale`.  Results are 32-bit.  A block
+//     takes 64 tokens of one unit; only a sequence's first block touches its stored inputs (a chunk is longer than any
+//     history), reads them for its first tokens and then brings them up to date.
 //
 // (3) The recurrences (`llm_wkv_recurrent`, `llm_delta_rule_recurrent`), per head with S in R^(dim x vdim):
 //       wkv     o_t = (S + diag(u) k_t v_t^T)^T r_t;   S <- diag(w_t) S + k_t v_t^T;   w_t = exp(-exp(z_t + w0))
@@ -22,6 +24,15 @@
 // shared memory in 32-bit (decays, gates and step sizes formed there), walked on the registers, then normalised, gated
 // and stored by one warp per token.  The order of every sum depends on the sizes alone, so a token's result does not
 // depend on how its prompt was cut or on what else is in the batch.
+//
+// Long portions can also be walked segment by segment in parallel (a segment length given to the launchers).  Both
+// recurrences are linear in S: behind a segment, S_out = M S_in + L, where L is what the segment leaves from a zero state
+// and M its transition: diag(prod_t w_t) for wkv; for the delta rule the product of the g_t (I - beta_t k_t k_t^T), a
+// dim x dim matrix, which the same walk yields column by column when it starts from the identity with values of zero.
+// Pass A runs every segment but the last from zero (delta: also `dim` more columns from the identity) and leaves L and M;
+// a scan gives every segment the state it starts from, S_in(k + 1) = M_k S_in(k) + L_k; pass C runs the segments again
+// from those states and writes the outputs.  All of it 32-bit; sums are then grouped by segment, so results agree with
+// the one-pass form to rounding, not bit for bit (the 32-bit path keeps the one-pass form).
 #include "common.cuh"
 
 #define REC_TOKENS 16
@@ -73,6 +84,7 @@ struct ConvArgs {
 
 #define CONV_MAX_PER_LANE 16    // a unit has at most 32 * 16 channels
 #define CONV_MAX_TAPS 8
+#define CONV_CHUNK 64           // tokens per block; more than CONV_MAX_TAPS - 1, so only a sequence's first block reads stored inputs
 
 template <typename T>
 __global__ void __launch_bounds__(256) short_conv_units_kernel(ConvArgs a) {
@@ -80,7 +92,8 @@ __global__ void __launch_bounds__(256) short_conv_units_kernel(ConvArgs a) {
     pdl_wait();
     const int seq = blockIdx.x, unit = blockIdx.y;
     const int begin = a.q_start[seq], end = a.q_start[seq + 1];
-    if (begin >= end) return;
+    const int chunk_begin = begin + blockIdx.z * CONV_CHUNK, chunk_end = min(end, chunk_begin + CONV_CHUNK);
+    if (chunk_begin >= end) return;
     const bool normed = unit < a.n_unit_norm;
     const int size = normed ? a.unit_dim : a.plain_dim;
     const int first = normed ? unit * a.unit_dim : a.n_unit_norm * a.unit_dim + (unit - a.n_unit_norm) * a.plain_dim;
@@ -88,7 +101,7 @@ __global__ void __launch_bounds__(256) short_conv_units_kernel(ConvArgs a) {
     const int history = a.taps - 1;
     const T* x = (const T*)a.x + a.column + first;
     float* state = a.state + (size_t)a.state_slots[seq] * max(history, 1) * a.channels + first;
-    for (int t = begin + warp; t < end; t += warps) {
+    for (int t = chunk_begin + warp; t < chunk_end; t += warps) {
         float y[CONV_MAX_PER_LANE];
         float squares = 0.0f;
 #pragma unroll
@@ -118,7 +131,8 @@ __global__ void __launch_bounds__(256) short_conv_units_kernel(ConvArgs a) {
             if (c < size) a.out[(size_t)t * a.channels + first + c] = y[u] * factor;
         }
     }
-    __syncthreads();      // every read of the stored inputs is done
+    if (blockIdx.z != 0) return;
+    __syncthreads();      // every read of the stored inputs is done (they are read by this block alone)
     // the new stored inputs: the last `history` of (old stored inputs, this step's inputs); a channel is one thread's,
     // which walks its rows oldest first, so a row is read before it is overwritten
     const int length = end - begin;
@@ -132,10 +146,10 @@ __global__ void __launch_bounds__(256) short_conv_units_kernel(ConvArgs a) {
 }
 
 LLM_EXPORT int llm_short_conv_units(const void* x, int row_width, int column, const float* taps_w, int taps, float* state,
-                                    const int* state_slots, const int* q_start, float* out, int n_seqs, int n_unit_norm,
+                                    const int* state_slots, const int* q_start, float* out, int n_seqs, int longest, int n_unit_norm,
                                     int unit_dim, int n_scaled, int n_plain, int plain_dim, float norm_eps, float scale, int dtype,
                                     cudaStream_t stream) {
-    if (n_seqs == 0) return LLM_OK;
+    if (n_seqs == 0 || longest <= 0) return LLM_OK;
     if (taps < 1 || taps > CONV_MAX_TAPS || unit_dim > 32 * CONV_MAX_PER_LANE || plain_dim > 32 * CONV_MAX_PER_LANE ||
         n_unit_norm < 0 || n_plain < 0 || n_unit_norm + n_plain == 0) {
         llm_set_error("short_conv_units: %d taps (1 to %d) over units of %d and %d channels (up to %d) are not supported", taps,
@@ -148,7 +162,7 @@ LLM_EXPORT int llm_short_conv_units(const void* x, int row_width, int column, co
     a.channels = n_unit_norm * unit_dim + n_plain * plain_dim;
     a.n_unit_norm = n_unit_norm; a.unit_dim = unit_dim; a.n_scaled = n_scaled; a.n_plain = n_plain; a.plain_dim = plain_dim;
     a.norm_eps = norm_eps; a.scale = scale;
-    LLM_DISPATCH_DTYPE(dtype, (llm_launch(short_conv_units_kernel<T>, dim3(n_seqs, n_unit_norm + n_plain), 256, 0, stream, a)));
+    LLM_DISPATCH_DTYPE(dtype, (llm_launch(short_conv_units_kernel<T>, dim3(n_seqs, n_unit_norm + n_plain, (longest + CONV_CHUNK - 1) / CONV_CHUNK), 256, 0, stream, a)));
     return llm_check_launch("short_conv_units");
 }
 
@@ -177,19 +191,42 @@ struct RecArgs {
     const void* h;
     float* shift_state;     // [slots, width]
     int width;
+    // segmented form
+    int segment, max_segments;  // tokens per segment, segments the scratch has room for per sequence
+    int groups;                 // delta, pass A: blocks per (segment, head): one for the value columns + those for the transition's
+    float* segment_state;       // [S, max_segments, heads, dim, vdim]: pass A leaves L there, the scan S_in
+    float* segment_move;        // wkv: [S, max_segments, heads, dim], the products of the decays; delta: [.., heads, dim, dim]
 };
 
 enum : int { REC_WKV = 0, REC_DELTA = 1 };
+// PASS 0: a sequence's tokens in one pass, from and into its state slot.  1: pass A of the segmented form.  3: pass C.
+enum : int { REC_ONE_PASS = 0, REC_LOCAL = 1, REC_OUTPUT = 3 };
 
-template <typename T, typename W, int R, int MODE>
+template <typename T, typename W, int R, int MODE, int PASS>
 __global__ void __launch_bounds__(512, 1) matrix_recurrence_kernel(RecArgs a) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float4 rec_shared_raw[];
     float* shared = reinterpret_cast<float*>(rec_shared_raw);
     const int seq = blockIdx.x, head = blockIdx.y;
-    const int begin = a.q_start[seq], end = a.q_start[seq + 1];
+    int begin = a.q_start[seq], end = a.q_start[seq + 1];
     if (begin >= end) return;
+    const int seq_end = end;
+    bool last_segment = true;
+    size_t segment_index = 0;
+    int group = 0;      // delta, pass A: 0: the value columns; g > 0: columns (g - 1) vdim ... of the transition
+    if (PASS != REC_ONE_PASS) {
+        const int segments = (end - begin + a.segment - 1) / a.segment;
+        const int groups = (PASS == REC_LOCAL && MODE == REC_DELTA) ? a.groups : 1;
+        const int segment = blockIdx.z / groups;
+        group = blockIdx.z % groups;
+        if (segment >= segments) return;
+        last_segment = segment == segments - 1;
+        if (PASS == REC_LOCAL && last_segment) return;      // nobody needs what a zero start leaves behind the last one
+        begin += segment * a.segment;
+        end = min(end, begin + a.segment);
+        segment_index = ((size_t)seq * a.max_segments + segment) * a.heads + head;
+    }
     const int dim = a.dim, vdim = a.vdim, P = a.partitions, padded = P * a.stride_rows;
     float* q_s = shared;                               // [REC_TOKENS][padded]   wkv: r
     float* k_s = q_s + REC_TOKENS * padded;
@@ -201,14 +238,22 @@ __global__ void __launch_bounds__(512, 1) matrix_recurrence_kernel(RecArgs a) {
     const int per_warp = 32 / P;                       // columns of S per warp
     const int part = lane / per_warp, column = warp * per_warp + lane % per_warp;
     const int row0 = part * R;
-    const bool owner = column < vdim;
+    const int move_column = (group - 1) * vdim + column;      // this thread's column of the transition (group > 0)
+    const bool owner = column < vdim && (group == 0 || move_column < dim);
     const T* proj = (const T*)a.proj;
     const int slot = a.state_slots[seq];
 
     float S[R];
+    float decay[(PASS == REC_LOCAL && MODE == REC_WKV) ? R : 1];      // pass A: the product of the segment's decays, row by row
     float* state = a.state + ((size_t)slot * a.heads + head) * dim * vdim;
+    float* segment_state = a.segment_state + segment_index * dim * vdim;
+    const float* source = PASS == REC_OUTPUT ? segment_state : state;
 #pragma unroll
-    for (int i = 0; i < R; ++i) S[i] = (owner && row0 + i < dim) ? state[(size_t)(row0 + i) * vdim + column] : 0.0f;
+    for (int i = 0; i < R; ++i) {
+        if (PASS == REC_LOCAL) S[i] = (group > 0 && row0 + i == move_column) ? 1.0f : 0.0f;
+        else S[i] = (owner && row0 + i < dim) ? source[(size_t)(row0 + i) * vdim + column] : 0.0f;
+        if (PASS == REC_LOCAL && MODE == REC_WKV) decay[i] = 1.0f;
+    }
 
     const int qk_head = MODE == REC_DELTA ? head / (a.heads / a.qk_heads) : head;
     for (int first = begin; first < end; first += REC_TOKENS) {
@@ -223,12 +268,14 @@ __global__ void __launch_bounds__(512, 1) matrix_recurrence_kernel(RecArgs a) {
                 if (i < dim) {
                     if (MODE == REC_WKV) {
                         const T* row = proj + token * a.row_width;
-                        qv = Num<T>::load(row + a.r_offset + head * dim + i);
                         kv = Num<T>::load(row + a.k_offset + head * dim + i);
                         wv = expf(-expf(a.wide[token * a.heads * dim + head * dim + i] + a.w0[head * dim + i]));
-                        bonus = fmaf(qv * a.bonus[head * dim + i], kv, bonus);
+                        if (PASS != REC_LOCAL) {
+                            qv = Num<T>::load(row + a.r_offset + head * dim + i);
+                            bonus = fmaf(qv * a.bonus[head * dim + i], kv, bonus);
+                        }
                     } else {
-                        qv = a.pre[token * a.pre_width + a.q_col + qk_head * dim + i];
+                        if (PASS != REC_LOCAL) qv = a.pre[token * a.pre_width + a.q_col + qk_head * dim + i];
                         kv = a.pre[token * a.pre_width + a.k_col + qk_head * dim + i];
                     }
                 }
@@ -238,8 +285,9 @@ __global__ void __launch_bounds__(512, 1) matrix_recurrence_kernel(RecArgs a) {
                 if (MODE == REC_WKV) w_s[at] = wv;
             }
             for (int j = lane; j < vdim; j += 32)
-                v_s[t * vdim + j] = MODE == REC_WKV ? Num<T>::load(proj + token * a.row_width + a.v_offset + head * vdim + j)
-                                                     : a.pre[token * a.pre_width + a.v_col + head * vdim + j];
+                v_s[t * vdim + j] = group > 0 ? 0.0f
+                                    : MODE == REC_WKV ? Num<T>::load(proj + token * a.row_width + a.v_offset + head * vdim + j)
+                                                      : a.pre[token * a.pre_width + a.v_col + head * vdim + j];
             if (MODE == REC_WKV) {
                 bonus = warp_sum(bonus);
                 if (lane == 0) scalar_s[2 * t] = bonus;
@@ -259,6 +307,21 @@ __global__ void __launch_bounds__(512, 1) matrix_recurrence_kernel(RecArgs a) {
             float o;
             if (MODE == REC_WKV) {
                 const float4* w4 = reinterpret_cast<const float4*>(w_s + t * padded + part * a.stride_rows);
+                if (PASS == REC_LOCAL) {
+#pragma unroll
+                    for (int i = 0; i < R / 4; ++i) {
+                        const float4 kk = k4[i], ww = w4[i];
+                        S[4 * i + 0] = fmaf(ww.x, S[4 * i + 0], kk.x * vj);
+                        S[4 * i + 1] = fmaf(ww.y, S[4 * i + 1], kk.y * vj);
+                        S[4 * i + 2] = fmaf(ww.z, S[4 * i + 2], kk.z * vj);
+                        S[4 * i + 3] = fmaf(ww.w, S[4 * i + 3], kk.w * vj);
+                        decay[(4 * i + 0) % (sizeof(decay) / sizeof(float))] *= ww.x;
+                        decay[(4 * i + 1) % (sizeof(decay) / sizeof(float))] *= ww.y;
+                        decay[(4 * i + 2) % (sizeof(decay) / sizeof(float))] *= ww.z;
+                        decay[(4 * i + 3) % (sizeof(decay) / sizeof(float))] *= ww.w;
+                    }
+                    continue;
+                }
                 float sum = 0.0f;
 #pragma unroll
                 for (int i = 0; i < R / 4; ++i) {
@@ -288,6 +351,17 @@ __global__ void __launch_bounds__(512, 1) matrix_recurrence_kernel(RecArgs a) {
                 for (int offset = per_warp; offset < 32; offset <<= 1) read += __shfl_xor_sync(0xffffffffu, read, offset);
                 const float d = beta * (vj - g * read);
                 asm volatile("" ::: "memory");      // the keys are read again below rather than held in registers meanwhile
+                if (PASS == REC_LOCAL) {
+#pragma unroll
+                    for (int i = 0; i < R / 4; ++i) {
+                        const float4 kk = k4[i];
+                        S[4 * i + 0] = fmaf(g, S[4 * i + 0], kk.x * d);
+                        S[4 * i + 1] = fmaf(g, S[4 * i + 1], kk.y * d);
+                        S[4 * i + 2] = fmaf(g, S[4 * i + 2], kk.z * d);
+                        S[4 * i + 3] = fmaf(g, S[4 * i + 3], kk.w * d);
+                    }
+                    continue;
+                }
                 float sum = 0.0f;
 #pragma unroll
                 for (int i = 0; i < R / 4; ++i) {
@@ -306,6 +380,7 @@ __global__ void __launch_bounds__(512, 1) matrix_recurrence_kernel(RecArgs a) {
             }
             if (owner && part == 0) o_s[t * vdim + column] = o;
         }
+        if (PASS == REC_LOCAL) continue;
         __syncthreads();
         // ---- head norm, gate, store: a warp per token
         for (int t = warp; t < count; t += warps) {
@@ -321,6 +396,26 @@ __global__ void __launch_bounds__(512, 1) matrix_recurrence_kernel(RecArgs a) {
             }
         }
     }
+    if (PASS == REC_LOCAL) {
+        if (owner && group == 0) {
+#pragma unroll
+            for (int i = 0; i < R; ++i)
+                if (row0 + i < dim) segment_state[(size_t)(row0 + i) * vdim + column] = S[i];
+        }
+        if (MODE == REC_DELTA && owner && group > 0) {
+            float* move = a.segment_move + segment_index * dim * dim;
+#pragma unroll
+            for (int i = 0; i < R; ++i)
+                if (row0 + i < dim) move[(size_t)(row0 + i) * dim + move_column] = S[i];
+        }
+        if (MODE == REC_WKV && column == 0) {
+#pragma unroll
+            for (int i = 0; i < R; ++i)
+                if (row0 + i < dim) a.segment_move[segment_index * dim + row0 + i] = decay[i % (sizeof(decay) / sizeof(float))];
+        }
+        return;
+    }
+    if (!last_segment) return;
     if (owner) {
 #pragma unroll
         for (int i = 0; i < R; ++i)
@@ -328,9 +423,110 @@ __global__ void __launch_bounds__(512, 1) matrix_recurrence_kernel(RecArgs a) {
     }
     if (MODE == REC_WKV && a.shift_state) {
         // the sequence's last row of this step is what its next token mixes with; the heads share the copy
-        const T* last = (const T*)a.h + (size_t)(end - 1) * a.width;
+        const T* last = (const T*)a.h + (size_t)(seq_end - 1) * a.width;
         for (int c = head * blockDim.x + threadIdx.x; c < a.width; c += a.heads * blockDim.x)
             a.shift_state[(size_t)slot * a.width + c] = Num<T>::load(last + c);
+    }
+}
+
+// The scan between the passes, per (sequence, head): S_in(0) is the slot's state and S_in(k + 1) = M_k S_in(k) + L_k; S_in(k)
+// takes L_k's place in the scratch.  With a diagonal M (wkv) the cells are independent: one thread per cell, the
+// segments' values loaded a few ahead of the chain of multiply-adds that needs them.
+__global__ void rec_scan_diagonal_kernel(RecArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    const int seq = blockIdx.x, head = blockIdx.y;
+    const int tokens = a.q_start[seq + 1] - a.q_start[seq];
+    if (tokens <= 0) return;
+    const int segments = (tokens + a.segment - 1) / a.segment;
+    const int cells = a.dim * a.vdim;
+    const int cell = blockIdx.z * blockDim.x + threadIdx.x;
+    if (cell >= cells) return;
+    const int row = cell / a.vdim;
+    float S = a.state[((size_t)a.state_slots[seq] * a.heads + head) * cells + cell];
+    const size_t first = ((size_t)seq * a.max_segments) * a.heads + head;
+    const size_t stride = a.heads;      // from one segment's index to the next's
+    constexpr int AHEAD = 4;
+    for (int k0 = 0; k0 < segments; k0 += AHEAD) {
+        float local[AHEAD], decay[AHEAD];
+#pragma unroll
+        for (int u = 0; u < AHEAD; ++u) {
+            const int k = k0 + u;
+            const bool more = k + 1 < segments;
+            const size_t index = first + (size_t)k * stride;
+            local[u] = more ? a.segment_state[index * cells + cell] : 0.0f;
+            decay[u] = more ? a.segment_move[index * a.dim + row] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < AHEAD; ++u) {
+            const int k = k0 + u;
+            if (k < segments) {
+                a.segment_state[(first + (size_t)k * stride) * cells + cell] = S;
+                if (k + 1 < segments) S = fmaf(decay[u], S, local[u]);
+            }
+        }
+    }
+}
+
+// With a full M (the delta rule) a column of S_in(k + 1) needs the whole column of S_in(k): a block keeps `chunk` columns
+// of the running state in shared memory, a thread up to SCAN_CELLS cells of them, each a sum over dim in a fixed order.
+#define SCAN_CELLS 8
+#define SCAN_THREADS 256
+__global__ void __launch_bounds__(SCAN_THREADS) rec_scan_matrix_kernel(RecArgs a, int chunk) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float4 scan_shared_raw[];
+    float* running = reinterpret_cast<float*>(scan_shared_raw);      // [dim][chunk]
+    const int seq = blockIdx.x, head = blockIdx.y, column0 = blockIdx.z * chunk;
+    const int tokens = a.q_start[seq + 1] - a.q_start[seq];
+    if (tokens <= 0) return;
+    const int segments = (tokens + a.segment - 1) / a.segment;
+    const int dim = a.dim, vdim = a.vdim;
+    const int columns = min(chunk, vdim - column0);
+    const float* state = a.state + ((size_t)a.state_slots[seq] * a.heads + head) * dim * vdim;
+    const size_t first = ((size_t)seq * a.max_segments) * a.heads + head;
+    float S[SCAN_CELLS], local[SCAN_CELLS];
+    int row[SCAN_CELLS], col[SCAN_CELLS];
+    bool valid[SCAN_CELLS];
+#pragma unroll
+    for (int u = 0; u < SCAN_CELLS; ++u) {
+        const int e = threadIdx.x + u * SCAN_THREADS;
+        row[u] = e / chunk;
+        col[u] = e % chunk;
+        valid[u] = row[u] < dim && col[u] < columns;
+        S[u] = valid[u] ? state[(size_t)row[u] * vdim + column0 + col[u]] : 0.0f;
+    }
+    for (int k = 0; k < segments; ++k) {
+        const size_t index = first + (size_t)k * a.heads;
+        float* segment_state = a.segment_state + index * dim * vdim;
+        const float* move = a.segment_move + index * dim * dim;
+        const bool more = k + 1 < segments;
+        __syncthreads();      // the running state of the segment before has been read
+#pragma unroll
+        for (int u = 0; u < SCAN_CELLS; ++u) {
+            if (!valid[u]) continue;
+            float* cell = segment_state + (size_t)row[u] * vdim + column0 + col[u];
+            local[u] = more ? *cell : 0.0f;
+            *cell = S[u];
+            running[row[u] * chunk + col[u]] = S[u];
+        }
+        __syncthreads();
+        if (!more) break;
+#pragma unroll
+        for (int u = 0; u < SCAN_CELLS; ++u) {
+            if (!valid[u]) continue;
+            const float* m_row = move + (size_t)row[u] * dim;
+            float part[4] = {local[u], 0.0f, 0.0f, 0.0f};
+            int m = 0;
+            for (; m + 4 <= dim; m += 4) {
+                part[0] = fmaf(m_row[m + 0], running[(m + 0) * chunk + col[u]], part[0]);
+                part[1] = fmaf(m_row[m + 1], running[(m + 1) * chunk + col[u]], part[1]);
+                part[2] = fmaf(m_row[m + 2], running[(m + 2) * chunk + col[u]], part[2]);
+                part[3] = fmaf(m_row[m + 3], running[(m + 3) * chunk + col[u]], part[3]);
+            }
+            for (; m < dim; ++m) part[0] = fmaf(m_row[m], running[m * chunk + col[u]], part[0]);
+            S[u] = (part[0] + part[1]) + (part[2] + part[3]);
+        }
     }
 }
 
@@ -358,6 +554,11 @@ LLM_EXPORT int llm_matrix_recurrence_supports(int dim, int vdim) {
 
 static int rec_launch(RecArgs& a, int mode, int n_seqs, int dtype, int weight_dtype, cudaStream_t stream) {
     if (n_seqs == 0) return LLM_OK;
+    const bool segmented = a.segment > 0;
+    if (segmented && (a.max_segments <= 0 || !a.segment_state || !a.segment_move)) {
+        llm_set_error("matrix recurrence: the segmented form needs its scratch");
+        return LLM_REFUSED;
+    }
     int partitions = 0;
     const int rows = a.heads > 0 ? rec_rows_per_thread(a.dim, a.vdim, &partitions) : 0;
     if (!rows) {
@@ -370,14 +571,36 @@ static int rec_launch(RecArgs& a, int mode, int n_seqs, int dtype, int weight_dt
     const int threads = (a.vdim + per_warp - 1) / per_warp * 32;
     const int padded = partitions * a.stride_rows;
     const size_t shared = ((size_t)(mode == REC_WKV ? 3 : 2) * REC_TOKENS * padded + (size_t)2 * REC_TOKENS * a.vdim + 2 * REC_TOKENS) * sizeof(float);
-    dim3 grid(n_seqs, a.heads);
-#define REC_LAUNCH(R, MODE)                                                                                                \
+    a.groups = 1 + (a.dim + a.vdim - 1) / a.vdim;
+    // the scan of the delta rule: columns per block such that a thread has at most SCAN_CELLS cells
+    int chunk = SCAN_CELLS * SCAN_THREADS / a.dim;
+    if (chunk > 8) chunk = 8;
+    if (chunk > a.vdim) chunk = a.vdim;
+    if (segmented && mode == REC_DELTA && chunk < 1) {
+        llm_set_error("matrix recurrence: the segmented delta rule takes heads of up to %d key channels", SCAN_CELLS * SCAN_THREADS);
+        return LLM_REFUSED;
+    }
+#define REC_LAUNCH_PASS(R, MODE, PASS, GRID)                                                                               \
     do {                                                                                                                   \
         if (shared > 40 * 1024) {                                                                                          \
-            const int status = llm_raise_shared_limit((const void*)matrix_recurrence_kernel<T, W, R, MODE>, shared, "matrix recurrence"); \
+            const int status = llm_raise_shared_limit((const void*)matrix_recurrence_kernel<T, W, R, MODE, PASS>, shared, "matrix recurrence"); \
             if (status != LLM_OK) return status;                                                                           \
         }                                                                                                                  \
-        llm_launch(matrix_recurrence_kernel<T, W, R, MODE>, grid, threads, shared, stream, a);                             \
+        llm_launch(matrix_recurrence_kernel<T, W, R, MODE, PASS>, GRID, threads, shared, stream, a);                       \
+    } while (0)
+#define REC_LAUNCH(R, MODE)                                                                                                \
+    do {                                                                                                                   \
+        if (!segmented) {                                                                                                  \
+            REC_LAUNCH_PASS(R, MODE, REC_ONE_PASS, dim3(n_seqs, a.heads));                                                 \
+        } else {                                                                                                           \
+            REC_LAUNCH_PASS(R, MODE, REC_LOCAL, dim3(n_seqs, a.heads, a.max_segments * (MODE == REC_DELTA ? a.groups : 1))); \
+            if (MODE == REC_WKV)                                                                                           \
+                llm_launch(rec_scan_diagonal_kernel, dim3(n_seqs, a.heads, (a.dim * a.vdim + 255) / 256), 256, 0, stream, a); \
+            else                                                                                                           \
+                llm_launch(rec_scan_matrix_kernel, dim3(n_seqs, a.heads, (a.vdim + chunk - 1) / chunk), SCAN_THREADS,      \
+                           (size_t)a.dim * chunk * sizeof(float), stream, a, chunk);                                       \
+            REC_LAUNCH_PASS(R, MODE, REC_OUTPUT, dim3(n_seqs, a.heads, a.max_segments));                                   \
+        }                                                                                                                  \
     } while (0)
 #define REC_LAUNCH_ROWS(MODE)                                                                                              \
     do {                                                                                                                   \
@@ -392,14 +615,17 @@ static int rec_launch(RecArgs& a, int mode, int n_seqs, int dtype, int weight_dt
     });
 #undef REC_LAUNCH_ROWS
 #undef REC_LAUNCH
+#undef REC_LAUNCH_PASS
     return llm_check_launch("matrix recurrence");
 }
 
 LLM_EXPORT int llm_wkv_recurrent(const void* proj, int row_width, int r_offset, int k_offset, int v_offset, int g_offset,
                                  const float* z, const float* w0, const float* bonus, const void* weight, float* state,
                                  const int* state_slots, const int* q_start, void* out, int n_seqs, int heads, int dim, float eps,
-                                 const void* h, float* shift_state, int width, int dtype, int weight_dtype, cudaStream_t stream) {
+                                 const void* h, float* shift_state, int width, int dtype, int weight_dtype, int segment, int max_segments,
+                                 float* segment_state, float* segment_move, cudaStream_t stream) {
     RecArgs a = {};
+    a.segment = segment; a.max_segments = max_segments; a.segment_state = segment_state; a.segment_move = segment_move;
     a.proj = proj; a.row_width = row_width; a.r_offset = r_offset; a.k_offset = k_offset; a.v_offset = v_offset; a.g_offset = g_offset;
     a.wide = z; a.w0 = w0; a.bonus = bonus; a.weight = weight; a.weight_stride = dim; a.state = state; a.state_slots = state_slots;
     a.q_start = q_start; a.out = out; a.heads = heads; a.dim = dim; a.vdim = dim; a.eps = eps; a.h = h; a.shift_state = shift_state;
@@ -411,6 +637,7 @@ LLM_EXPORT int llm_delta_rule_recurrent(const void* proj, int row_width, int g_o
                                         int k_col, int v_col, const float* wide, const float* a_log, const float* dt_bias,
                                         const void* weight, float* state, const int* state_slots, const int* q_start, void* out,
                                         int n_seqs, int heads, int qk_heads, int dim, int vdim, float eps, int dtype, int weight_dtype,
+                                        int segment, int max_segments, float* segment_state, float* segment_move,
                                         cudaStream_t stream) {
     if (qk_heads <= 0 || heads % qk_heads) {
         llm_set_error("delta_rule_recurrent: %d heads are no multiple of %d query/key heads", heads, qk_heads);
@@ -419,6 +646,7 @@ LLM_EXPORT int llm_delta_rule_recurrent(const void* proj, int row_width, int g_o
     RecArgs a = {};
     a.proj = proj; a.row_width = row_width; a.g_offset = g_offset; a.pre = pre; a.pre_width = pre_width; a.q_col = q_col;
     a.k_col = k_col; a.v_col = v_col; a.qk_heads = qk_heads; a.wide = wide; a.a_log = a_log; a.dt_bias = dt_bias; a.weight = weight;
+    a.segment = segment; a.max_segments = max_segments; a.segment_state = segment_state; a.segment_move = segment_move;
     a.weight_stride = 0; a.state = state; a.state_slots = state_slots; a.q_start = q_start; a.out = out; a.heads = heads;
     a.dim = dim; a.vdim = vdim; a.eps = eps;
     return rec_launch(a, REC_DELTA, n_seqs, dtype, weight_dtype, stream);

@@ -514,8 +514,8 @@ def short_conv_units(x: torch.Tensor, column: int, taps_w: torch.Tensor, state: 
         raise KernelError(f"the convolution state must be [slots, {max(taps - 1, 1)}, {channels}], got {tuple(state.shape)}")
     out = torch.empty((tokens, channels), dtype=torch.float32, device=x.device)
     call("llm_short_conv_units", x.data_ptr(), row_width, int(column), taps_w.data_ptr(), int(taps), state.data_ptr(),
-         batch.state_slots.data_ptr(), batch.q_start.data_ptr(), out.data_ptr(), batch.n_seqs, int(n_unit_norm), int(unit_dim),
-         int(n_scaled), int(n_plain), int(plain_dim), float(norm_eps), float(scale), dtype_code(x.dtype), stream_handle())
+         batch.state_slots.data_ptr(), batch.q_start.data_ptr(), out.data_ptr(), batch.n_seqs, int(batch.max_q_len), int(n_unit_norm),
+         int(unit_dim), int(n_scaled), int(n_plain), int(plain_dim), float(norm_eps), float(scale), dtype_code(x.dtype), stream_handle())
     return out
 
 
@@ -525,7 +525,7 @@ def matrix_recurrence_supported(dim: int, value_dim: int) -> bool:
 
 def wkv_recurrent(rkvg: torch.Tensor, z: torch.Tensor, w0: torch.Tensor, bonus: torch.Tensor, weight: torch.Tensor,
                   state: torch.Tensor, batch, heads: int, dim: int, eps: float, h: Optional[torch.Tensor] = None,
-                  shift_state: Optional[torch.Tensor] = None) -> torch.Tensor:
+                  shift_state: Optional[torch.Tensor] = None, segment: Optional[int] = None) -> torch.Tensor:
     """The recurrence with a per-channel decay and a bonus for the current token, sequence by sequence, from and into each
     sequence's slot of ``state`` (float32 [slots, heads, dim, dim]):
 
@@ -535,7 +535,8 @@ def wkv_recurrent(rkvg: torch.Tensor, z: torch.Tensor, w0: torch.Tensor, bonus: 
     ``rkvg`` is [4, N, heads * dim] (r, k, v and the gate's pre-activation) in the activation type, ``z`` float32
     [N, heads * dim], ``w0`` float32 [heads * dim], ``bonus`` (u) float32 [heads, dim], ``weight`` [heads * dim].  With
     ``h`` and ``shift_state`` the sequence's last row of ``h`` is left in its slot of ``shift_state`` for the next step's
-    ``token_shift_mix``.  Returns [N, heads * dim] in the activation type; the recurrence itself is 32-bit."""
+    ``token_shift_mix``.  Returns [N, heads * dim] in the activation type; the recurrence itself is 32-bit.  ``segment`` as
+    for ``delta_rule_recurrent``."""
     check(rkvg, "r, k, v and gate", last_dim=heads * dim)
     if rkvg.dim() != 3 or rkvg.shape[0] != 4:
         raise KernelError(f"r, k, v and the gate come as [4, N, {heads * dim}], got {tuple(rkvg.shape)}")
@@ -556,16 +557,46 @@ def wkv_recurrent(rkvg: torch.Tensor, z: torch.Tensor, w0: torch.Tensor, bonus: 
         width = h.shape[1]
         check(shift_state, "shift state", torch.float32, width)
     out = torch.empty((tokens, heads * dim), dtype=rkvg.dtype, device=rkvg.device)
+    segment, segments, segment_state, segment_move = _recurrence_segments(batch, rkvg, segment, heads, dim, dim, dim)
     call("llm_wkv_recurrent", rkvg.data_ptr(), heads * dim, 0, plane, 2 * plane, 3 * plane, z.data_ptr(), w0.data_ptr(),
          bonus.data_ptr(), weight.data_ptr(), state.data_ptr(), batch.state_slots.data_ptr(), batch.q_start.data_ptr(),
          out.data_ptr(), batch.n_seqs, int(heads), int(dim), float(eps), pointer(h), pointer(shift_state) if h is not None else 0,
-         int(width), dtype_code(rkvg.dtype), dtype_code(weight.dtype), stream_handle())
+         int(width), dtype_code(rkvg.dtype), dtype_code(weight.dtype), segment, segments, pointer(segment_state),
+         pointer(segment_move), stream_handle())
     return out
+
+
+REC_SEGMENT = 64                   # fewest tokens per segment of the segmented matrix recurrences
+REC_MAX_SEGMENTS = 64              # most segments per sequence
+REC_SCRATCH_BYTES = 1 << 30        # most scratch that the segments' states and transitions may take
+
+
+def _recurrence_segments(batch, activations: torch.Tensor, segment: Optional[int], heads: int, dim: int, value_dim: int,
+                         move_columns: int):
+    """Segment length, segments per sequence and the scratch of the segmented form of ``wkv_recurrent`` and
+    ``delta_rule_recurrent``: a state [dim, value_dim] and a transition (``move_columns`` values per key channel: 1 for a
+    diagonal one, dim for a full one) per (sequence, segment, head).  ``segment`` None: chosen here, for bfloat16 steps
+    whose longest portion spans several segments and whose scratch stays within REC_SCRATCH_BYTES; 0: the one-pass form."""
+    longest = int(batch.max_q_len)
+    per_segment = batch.n_seqs * heads * dim * (value_dim + move_columns) * 4
+    if segment is None:
+        most = min(REC_MAX_SEGMENTS, REC_SCRATCH_BYTES // max(per_segment, 1))
+        segment = 0 if activations.dtype != torch.bfloat16 or longest < 2 * REC_SEGMENT or most < 2 else max(REC_SEGMENT, -(-longest // most))
+    if not segment:
+        return 0, 0, None, None
+    segments = -(-longest // int(segment))
+    key = ("matrix_recurrence_segments", batch.n_seqs, segments, heads, dim, value_dim, move_columns)
+    scratch = batch.scratch.get(key)
+    if scratch is None:
+        scratch = (torch.empty((batch.n_seqs, segments, heads, dim, value_dim), dtype=torch.float32, device=activations.device),
+                   torch.empty((batch.n_seqs, segments, heads, dim, move_columns), dtype=torch.float32, device=activations.device))
+        batch.scratch[key] = scratch
+    return int(segment), segments, scratch[0], scratch[1]
 
 
 def delta_rule_recurrent(proj: torch.Tensor, g_column: int, pre: torch.Tensor, wide: torch.Tensor, a_log: torch.Tensor,
                          dt_bias: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, batch, heads: int, qk_heads: int,
-                         dim: int, value_dim: int, eps: float) -> torch.Tensor:
+                         dim: int, value_dim: int, eps: float, segment: Optional[int] = None) -> torch.Tensor:
     """The gated delta rule, sequence by sequence, from and into each sequence's slot of ``state`` (float32
     [slots, heads, dim, value_dim]):
 
@@ -576,7 +607,12 @@ def delta_rule_recurrent(proj: torch.Tensor, g_column: int, pre: torch.Tensor, w
     ``pre`` is float32 [N, 2 * qk_heads * dim + heads * value_dim] = q | k | v as ``short_conv_units`` leaves them (head h
     reads q/k head h // (heads / qk_heads)); ``wide`` float32 [N, 2 heads] = b | a; ``a_log`` (A) and ``dt_bias`` float32
     [heads]; the gate's pre-activation is heads * value_dim columns of ``proj`` from ``g_column``.  Returns
-    [N, heads * value_dim] in the activation type; the recurrence itself is 32-bit."""
+    [N, heads * value_dim] in the activation type; the recurrence itself is 32-bit.
+
+    ``segment``: tokens per segment of the form that walks a long portion's segments in parallel: every segment from a
+    zero state, which also yields its transition; a scan that gives each segment the state it starts from; every segment
+    again for the outputs (results equal to rounding).  None: chosen for bfloat16 steps whose longest portion spans several
+    segments; 0: always the one-pass form, which is also what the 32-bit path runs."""
     check(proj, "packed projection")
     tokens, row_width = proj.shape
     if g_column < 0 or g_column + heads * value_dim > row_width:
@@ -592,10 +628,12 @@ def delta_rule_recurrent(proj: torch.Tensor, g_column: int, pre: torch.Tensor, w
     if pre.shape[0] != tokens or wide.shape[0] != tokens:
         raise KernelError("every input needs one row per token")
     out = torch.empty((tokens, heads * value_dim), dtype=proj.dtype, device=proj.device)
+    segment, segments, segment_state, segment_move = _recurrence_segments(batch, proj, segment, heads, dim, value_dim, dim)
     call("llm_delta_rule_recurrent", proj.data_ptr(), row_width, int(g_column), pre.data_ptr(), pre.shape[1], 0, qk_heads * dim,
          2 * qk_heads * dim, wide.data_ptr(), a_log.data_ptr(), dt_bias.data_ptr(), weight.data_ptr(), state.data_ptr(),
          batch.state_slots.data_ptr(), batch.q_start.data_ptr(), out.data_ptr(), batch.n_seqs, int(heads), int(qk_heads), int(dim),
-         int(value_dim), float(eps), dtype_code(proj.dtype), dtype_code(weight.dtype), stream_handle())
+         int(value_dim), float(eps), dtype_code(proj.dtype), dtype_code(weight.dtype), segment, segments, pointer(segment_state),
+         pointer(segment_move), stream_handle())
     return out
 
 

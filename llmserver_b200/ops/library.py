@@ -34,10 +34,10 @@ SIGNATURES = {
     "llm_gla_recurrent": [_P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _F, _F, _I, _I, _I, _I, _P, _P, _S],
     "llm_pointwise": [_I, _P, _P, _P, ctypes.c_longlong, _F, _F, _I, _I, _S],
     "llm_token_shift_mix": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _S],
-    "llm_short_conv_units": [_P, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _S],
+    "llm_short_conv_units": [_P, _I, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _S],
     "llm_matrix_recurrence_supports": [_I, _I],
-    "llm_wkv_recurrent": [_P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _P, _P, _I, _I, _I, _S],
-    "llm_delta_rule_recurrent": [_P, _I, _I, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _S],
+    "llm_wkv_recurrent": [_P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _P, _P, _I, _I, _I, _I, _I, _P, _P, _S],
+    "llm_delta_rule_recurrent": [_P, _I, _I, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P, _P, _S],
     "llm_moe_route": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _S],
     "llm_moe_select": [_P, _P, _P, _P, _I, _I, _I, _F, _S],
     "llm_indexed_linear": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _S],

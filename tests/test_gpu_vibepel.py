@@ -212,13 +212,16 @@ def test_token_shift_mix_reads_the_row_before_from_the_step_or_the_slot(dtype):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("taps,normed,unit,n_scaled,n_plain,plain_dim", [(4, 2, 16, 1, 2, 8), (2, 4, 24, 2, 1, 40), (5, 1, 40, 1, 3, 33),
                                                                         (3, 2, 128, 1, 2, 128), (1, 2, 8, 1, 1, 8), (4, 0, 8, 0, 2, 72)])
-def test_short_convolution_with_history_in_slots(dtype, taps, normed, unit, n_scaled, n_plain, plain_dim):
+@pytest.mark.parametrize("long", [False, True])
+def test_short_convolution_with_history_in_slots(dtype, taps, normed, unit, n_scaled, n_plain, plain_dim, long):
     """Three sequences: one continued from an earlier step by portions shorter than the convolution, one new, one a
     single token; the stored inputs behind the step are compared too, and nobody's slot stays as it is."""
     from llmserver_b200 import ops
     generator = torch.Generator().manual_seed(taps * 100 + unit)
     channels = normed * unit + n_plain * plain_dim
     lengths = [(0, 1), (1, 2), (3, 9)], [(0, 17)], [(0, 6), (6, 1)]
+    if long:      # portions that several blocks share: only the first reads the stored inputs, and only it renews them
+        lengths = [(0, 3), (3, 150), (153, 64)], [(0, 129)], [(0, 65), (65, 1)]
     slots = [2, 0, 3]
     x = [torch.randn((sum(now for _, now in steps), channels + 7), generator=generator).to(dtype) for steps in lengths]
     taps_w = (torch.randn((channels, taps), generator=generator) * 0.6).to(torch.bfloat16).float()
@@ -251,11 +254,13 @@ def test_short_convolution_with_history_in_slots(dtype, taps, normed, unit, n_sc
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("segment", [0, 5, 16])
 @pytest.mark.parametrize("heads,dim", [(2, 24), (5, 8), (1, 72), (3, 64), (2, 32), (1, 128), (2, 40)])
-def test_wkv_recurrence_kernel(dtype, heads, dim):
+def test_wkv_recurrence_kernel(dtype, heads, dim, segment):
     """Three sequences in one step: one continues from a state that an earlier step left (in another slot order), one
     starts from zero, one is a single token.  Decays run from 'forgets at once' to 'keeps for hundreds of tokens'; the
-    state and the stored row behind the step are compared too."""
+    state and the stored row behind the step are compared too.  With ``segment`` the step's portions are walked segment
+    by segment in parallel (eight segments, three and one, the last ones shorter), which must give the same."""
     from llmserver_b200 import ops
     generator = torch.Generator().manual_seed(dim * 7 + heads)
     inner, width = heads * dim, 48
@@ -293,7 +298,8 @@ def test_wkv_recurrence_kernel(dtype, heads, dim):
     got = ops.wkv_recurrent(torch.cat([rkvg[s][:, before:] for s, (before, _) in enumerate(lengths)], dim=1).contiguous().to(DEVICE),
                             torch.cat([z[s][before:] for s, (before, _) in enumerate(lengths)]).to(DEVICE), w0.to(DEVICE), u.to(DEVICE),
                             weight.to(DEVICE), state, batch, heads, dim, eps,
-                            h=torch.cat([h[s][before:] for s, (before, _) in enumerate(lengths)]).to(DEVICE), shift_state=shift).cpu().double()
+                            h=torch.cat([h[s][before:] for s, (before, _) in enumerate(lengths)]).to(DEVICE), shift_state=shift,
+                            segment=segment).cpu().double()
     tolerance = 2e-5 if dtype == torch.float32 else 2e-2
     at = 0
     for s, (before, now) in enumerate(lengths):
@@ -308,7 +314,10 @@ def test_wkv_recurrence_kernel(dtype, heads, dim):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,qk_heads,dim,vdim", [(2, 1, 24, 40), (5, 5, 8, 16), (1, 1, 72, 33), (4, 2, 64, 128), (3, 1, 128, 64),
                                                      (2, 2, 128, 128), (6, 3, 16, 8), (2, 1, 40, 100)])
-def test_gated_delta_rule_kernel(dtype, heads, qk_heads, dim, vdim):
+@pytest.mark.parametrize("segment", [0, 5, 16])
+def test_gated_delta_rule_kernel(dtype, heads, qk_heads, dim, vdim, segment):
+    """As for the wkv recurrence.  The segmented form also needs every segment's transition, a dim x dim matrix that is
+    walked in groups of vdim columns: sizes with more, fewer and as many key channels as values are all here."""
     from llmserver_b200 import ops
     generator = torch.Generator().manual_seed(dim * 7 + vdim)
     keys, values = qk_heads * dim, heads * vdim
@@ -354,7 +363,8 @@ def test_gated_delta_rule_kernel(dtype, heads, qk_heads, dim, vdim):
     got = ops.delta_rule_recurrent(torch.cat([proj[s][before:] for s, (before, _) in enumerate(lengths)]).to(DEVICE), 3,
                                    torch.cat([pre[s][before:] for s, (before, _) in enumerate(lengths)]).to(DEVICE),
                                    torch.cat([wide[s][before:] for s, (before, _) in enumerate(lengths)]).to(DEVICE), a_log.to(DEVICE),
-                                   dt_bias.to(DEVICE), weight.to(DEVICE), state, batch, heads, qk_heads, dim, vdim, eps).cpu().double()
+                                   dt_bias.to(DEVICE), weight.to(DEVICE), state, batch, heads, qk_heads, dim, vdim, eps,
+                                   segment=segment).cpu().double()
     tolerance = 2e-5 if dtype == torch.float32 else 2e-2
     at = 0
     for s, (before, now) in enumerate(lengths):
@@ -407,6 +417,23 @@ def test_mixed_batches_reuse_pages_and_slots(folders, name, dtype):
             assert group.pool.allocations > group.pool.num_pages, "the trace was meant to reuse pages"
     # seven requests went through four state slots
     assert replayer.cache.slots.num_slots == 4 and len(replayer.cache.slots.free) == 4
+
+
+@pytest.mark.parametrize("name", NAMES)
+def test_portions_walked_by_short_segments(folders, name, monkeypatch):
+    """The recurrences walk a long portion's segments in parallel.  With segments of eight tokens every portion of sixteen
+    or more goes that way, beside shorter ones and single tokens that do not; the segments' ends fall anywhere."""
+    monkeypatch.setattr("llmserver_b200.ops.REC_SEGMENT", 8)
+    vocab = VIBEPEL[name][0]["vocab"]
+    tokens = tokens_for(vocab, 181, 11)
+    records = traces.portions("r", tokens, [17, 2, 16, 3, 41, 1, 70, 15])
+    got, _ = run_in_process(folders[name], "bfloat16", records, traces.rounded(len(tokens)), page_size=8)
+    compare(got, records, {"r": tokens}, folders[name], "bfloat16", f"{name} portions by segments")
+    lengths = {"r0": 110, "r1": 67, "r2": 40, "r3": 131}
+    requests = {key: tokens_for(vocab, length, 41 + index) for index, (key, length) in enumerate(lengths.items())}
+    records, peak = traces.mixed(requests, seed=6)
+    got, _ = run_in_process(folders[name], "bfloat16", records, peak)
+    compare(got, records, requests, folders[name], "bfloat16", f"{name} mixed by segments")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
