@@ -530,6 +530,100 @@ __global__ void __launch_bounds__(SCAN_THREADS) rec_scan_matrix_kernel(RecArgs a
     }
 }
 
+// The same scan for heads of up to SCAN_STAGED_DIM key channels (a multiple of four): the transition of the next segment
+// is copied into shared memory (cp.async, two buffers) while this segment's product runs from shared memory, a thread
+// one row of 4 * C4 columns.  The sum over the key channels runs in ascending order.
+#define SCAN_STAGED_DIM 128
+template <int C4>
+__global__ void __launch_bounds__(2 * SCAN_STAGED_DIM) rec_scan_matrix_staged_kernel(RecArgs a) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float4 scan_shared_raw[];
+    constexpr int CHUNK = 8 * C4;          // columns per block: two threads per row, 4 * C4 columns each
+    const int dim = a.dim, vdim = a.vdim, stride = dim + 4;
+    float* move_s = reinterpret_cast<float*>(scan_shared_raw);      // [2][dim][stride]
+    float* running = move_s + 2 * dim * stride;                     // [dim][CHUNK]
+    const int seq = blockIdx.x, head = blockIdx.y, column0 = blockIdx.z * CHUNK;
+    const int tokens = a.q_start[seq + 1] - a.q_start[seq];
+    if (tokens <= 0) return;
+    const int segments = (tokens + a.segment - 1) / a.segment;
+    const size_t first = ((size_t)seq * a.max_segments) * a.heads + head;
+    const int row = threadIdx.x >> 1, c0 = (threadIdx.x & 1) * (4 * C4);
+    const bool row_valid = row < dim;
+    const float* state = a.state + ((size_t)a.state_slots[seq] * a.heads + head) * dim * vdim;
+    float S[4 * C4], local[4 * C4];
+#pragma unroll
+    for (int j = 0; j < 4 * C4; ++j) {
+        const int column = column0 + c0 + j;
+        S[j] = (row_valid && column < vdim) ? state[(size_t)row * vdim + column] : 0.0f;
+    }
+    const int quads = dim * dim / 4;      // 16-byte pieces of a transition
+    auto fetch = [&](int k) {
+        const float* move = a.segment_move + (first + (size_t)k * a.heads) * dim * dim;
+        float* dst = move_s + (k & 1) * dim * stride;
+        for (int f = threadIdx.x; f < quads; f += blockDim.x) {
+            const int r = f / (dim / 4), c = (f % (dim / 4)) * 4;
+            const unsigned target = (unsigned)__cvta_generic_to_shared(dst + r * stride + c);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(target), "l"(move + (size_t)r * dim + c) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    // what segment k leaves from a zero state (nothing behind the last one); read a segment ahead of its use
+    auto read_local = [&](int k, float* into) {
+        const float* segment_state = a.segment_state + (first + (size_t)k * a.heads) * dim * vdim;
+#pragma unroll
+        for (int j = 0; j < 4 * C4; ++j) {
+            const int column = column0 + c0 + j;
+            into[j] = (k + 1 < segments && row_valid && column < vdim) ? segment_state[(size_t)row * vdim + column] : 0.0f;
+        }
+    };
+    float next_local[4 * C4];
+    if (segments > 1) fetch(0);
+    read_local(0, next_local);
+    for (int k = 0; k < segments; ++k) {
+        const bool more = k + 1 < segments, ahead = k + 2 < segments;
+        if (ahead) fetch(k + 1);
+        float* segment_state = a.segment_state + (first + (size_t)k * a.heads) * dim * vdim;
+#pragma unroll
+        for (int j = 0; j < 4 * C4; ++j) {
+            const int column = column0 + c0 + j;
+            local[j] = next_local[j];
+            if (row_valid && column < vdim) segment_state[(size_t)row * vdim + column] = S[j];
+        }
+        if (!more) break;
+        read_local(k + 1, next_local);
+        if (row_valid) {
+#pragma unroll
+            for (int c = 0; c < C4; ++c)
+                reinterpret_cast<float4*>(running + row * CHUNK + c0)[c] = make_float4(S[4 * c], S[4 * c + 1], S[4 * c + 2], S[4 * c + 3]);
+        }
+        if (ahead) asm volatile("cp.async.wait_group 1;" ::: "memory");
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();      // this segment's transition and the running state are in shared memory
+        if (row_valid) {
+            const float* m_row = move_s + (k & 1) * dim * stride + row * stride;
+#pragma unroll
+            for (int j = 0; j < 4 * C4; ++j) S[j] = local[j];
+            for (int m = 0; m < dim; m += 4) {
+                const float4 mm = *reinterpret_cast<const float4*>(m_row + m);
+                const float factor[4] = {mm.x, mm.y, mm.z, mm.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+#pragma unroll
+                    for (int c = 0; c < C4; ++c) {
+                        const float4 r = reinterpret_cast<const float4*>(running + (m + i) * CHUNK + c0)[c];
+                        S[4 * c + 0] = fmaf(factor[i], r.x, S[4 * c + 0]);
+                        S[4 * c + 1] = fmaf(factor[i], r.y, S[4 * c + 1]);
+                        S[4 * c + 2] = fmaf(factor[i], r.z, S[4 * c + 2]);
+                        S[4 * c + 3] = fmaf(factor[i], r.w, S[4 * c + 3]);
+                    }
+                }
+            }
+        }
+        __syncthreads();      // the running state and this buffer have been read
+    }
+}
+
 // Rows of S per thread and row partitions per warp (a power of two) for heads of `dim` x `vdim`: the fewest rows with
 // which a block has at most 512 threads; 0: no arrangement (64 rows per thread already spill some).
 static int rec_rows_per_thread(int dim, int vdim, int* partitions) {
@@ -550,6 +644,22 @@ static int rec_rows_per_thread(int dim, int vdim, int* partitions) {
 LLM_EXPORT int llm_matrix_recurrence_supports(int dim, int vdim) {
     int partitions;
     return dim > 0 && vdim > 0 && rec_rows_per_thread(dim, vdim, &partitions) != 0;
+}
+
+// The staged scan: 8 columns per block; 16 where blocks of 8 would be more than one per SM (its shared memory allows one).
+static int rec_launch_staged_scan(RecArgs& a, int n_seqs, cudaStream_t stream) {
+    const bool wide = (size_t)n_seqs * a.heads * ((a.vdim + 7) / 8) > 148;
+    const int chunk = wide ? 16 : 8;
+    const size_t shared = ((size_t)2 * a.dim * (a.dim + 4) + (size_t)a.dim * chunk) * sizeof(float);
+    const void* kernel = wide ? (const void*)rec_scan_matrix_staged_kernel<2> : (const void*)rec_scan_matrix_staged_kernel<1>;
+    if (shared > 40 * 1024) {
+        const int status = llm_raise_shared_limit(kernel, shared, "matrix recurrence scan");
+        if (status != LLM_OK) return status;
+    }
+    const dim3 grid(n_seqs, a.heads, (a.vdim + chunk - 1) / chunk);
+    if (wide) llm_launch(rec_scan_matrix_staged_kernel<2>, grid, 2 * SCAN_STAGED_DIM, shared, stream, a);
+    else llm_launch(rec_scan_matrix_staged_kernel<1>, grid, 2 * SCAN_STAGED_DIM, shared, stream, a);
+    return LLM_OK;
 }
 
 static int rec_launch(RecArgs& a, int mode, int n_seqs, int dtype, int weight_dtype, cudaStream_t stream) {
@@ -576,6 +686,7 @@ static int rec_launch(RecArgs& a, int mode, int n_seqs, int dtype, int weight_dt
     int chunk = SCAN_CELLS * SCAN_THREADS / a.dim;
     if (chunk > 8) chunk = 8;
     if (chunk > a.vdim) chunk = a.vdim;
+    const bool staged_scan = a.dim <= SCAN_STAGED_DIM && a.dim % 4 == 0;
     if (segmented && mode == REC_DELTA && chunk < 1) {
         llm_set_error("matrix recurrence: the segmented delta rule takes heads of up to %d key channels", SCAN_CELLS * SCAN_THREADS);
         return LLM_REFUSED;
@@ -596,7 +707,10 @@ static int rec_launch(RecArgs& a, int mode, int n_seqs, int dtype, int weight_dt
             REC_LAUNCH_PASS(R, MODE, REC_LOCAL, dim3(n_seqs, a.heads, a.max_segments * (MODE == REC_DELTA ? a.groups : 1))); \
             if (MODE == REC_WKV)                                                                                           \
                 llm_launch(rec_scan_diagonal_kernel, dim3(n_seqs, a.heads, (a.dim * a.vdim + 255) / 256), 256, 0, stream, a); \
-            else                                                                                                           \
+            else if (staged_scan) {                                                                                        \
+                const int status = rec_launch_staged_scan(a, n_seqs, stream);                                              \
+                if (status != LLM_OK) return status;                                                                       \
+            } else                                                                                                         \
                 llm_launch(rec_scan_matrix_kernel, dim3(n_seqs, a.heads, (a.vdim + chunk - 1) / chunk), SCAN_THREADS,      \
                            (size_t)a.dim * chunk * sizeof(float), stream, a, chunk);                                       \
             REC_LAUNCH_PASS(R, MODE, REC_OUTPUT, dim3(n_seqs, a.heads, a.max_segments));                                   \

@@ -313,11 +313,14 @@ def test_wkv_recurrence_kernel(dtype, heads, dim, segment):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,qk_heads,dim,vdim", [(2, 1, 24, 40), (5, 5, 8, 16), (1, 1, 72, 33), (4, 2, 64, 128), (3, 1, 128, 64),
-                                                     (2, 2, 128, 128), (6, 3, 16, 8), (2, 1, 40, 100)])
+                                                     (2, 2, 128, 128), (6, 3, 16, 8), (2, 1, 40, 100), (1, 1, 192, 48), (2, 1, 30, 20),
+                                                     (8, 2, 32, 128)])
 @pytest.mark.parametrize("segment", [0, 5, 16])
 def test_gated_delta_rule_kernel(dtype, heads, qk_heads, dim, vdim, segment):
     """As for the wkv recurrence.  The segmented form also needs every segment's transition, a dim x dim matrix that is
-    walked in groups of vdim columns: sizes with more, fewer and as many key channels as values are all here."""
+    walked in groups of vdim columns: sizes with more, fewer and as many key channels as values are all here, and sizes
+    for each of the scan's forms (key channels beyond what it stages in shared memory, or no multiple of four; enough heads
+    and values for its wider blocks)."""
     from llmserver_b200 import ops
     generator = torch.Generator().manual_seed(dim * 7 + vdim)
     keys, values = qk_heads * dim, heads * vdim
