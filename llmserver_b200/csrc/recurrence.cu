@@ -203,7 +203,7 @@ enum : int { REC_WKV = 0, REC_DELTA = 1 };
 enum : int { REC_ONE_PASS = 0, REC_LOCAL = 1, REC_OUTPUT = 3 };
 
 template <typename T, typename W, int R, int MODE, int PASS>
-__global__ void __launch_bounds__(512, 1) matrix_recurrence_kernel(RecArgs a) {
+__global__ void __launch_bounds__(512, R <= 8 ? 2 : 1) matrix_recurrence_kernel(RecArgs a) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float4 rec_shared_raw[];

@@ -378,6 +378,156 @@ def test_gated_delta_rule_kernel(dtype, heads, qk_heads, dim, vdim, segment):
     assert bool((state[1] == 7.0).all())
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("kind", ["wkv", "delta"])
+def test_recurrences_keep_a_far_key_across_portions_and_segments(dtype, kind):
+    """One pair of key and value is written at the third token; no later key has a part along it and nothing decays, and
+    only the last token, 700 tokens on, asks for it.  The sequence comes as a long portion (walked by segments in
+    bfloat16), a second one that ends in the middle of a segment, and a single token; the plain scan without the third
+    token's write gives a very different last row."""
+    from llmserver_b200 import ops
+    generator = torch.Generator().manual_seed(5)
+    heads, dim, vdim, total, portions = 2, 32, 32, 703, [(0, 300), (300, 402), (702, 1)]
+    k = torch.randn((total, heads, dim), generator=generator)
+    k[:, :, 0] = 0.0
+    k[2] = 0.0
+    k[2, :, 0] = 3.0
+    q = torch.randn((total, heads, dim), generator=generator) * 0.3
+    q[-1] = 0.0
+    q[-1, :, 0] = 3.0
+    v = torch.randn((total, heads, vdim), generator=generator)
+    if kind == "delta":
+        k = torch.nn.functional.normalize(k, dim=-1)
+    q, k, v = q.to(dtype).float(), k.to(dtype).float(), v.to(dtype).float()
+    gate = torch.randn((total, heads * vdim), generator=generator).to(dtype)
+    weight = torch.ones((heads * vdim,) if kind == "wkv" else (vdim,), dtype=dtype)
+    eps = 1e-5
+    if kind == "wkv":
+        z, w0, u = torch.full((total, heads * dim), -14.0), torch.zeros((heads * dim,)), torch.zeros((heads, dim))
+        w = torch.exp(-torch.exp(z.double())).view(total, heads, dim)
+    else:
+        wide = torch.cat([torch.full((total, heads), 1.0), torch.full((total, heads), -30.0)], dim=1)      # beta 0.73, g = 1
+        a_log, dt_bias = torch.zeros((heads,)), torch.zeros((heads,))
+        beta, g = torch.sigmoid(wide[:, :heads].double()), torch.ones((total, heads), dtype=F64)
+
+    def plain_run(drop):
+        out = torch.zeros((total, heads, vdim), dtype=F64)
+        for head in range(heads):
+            keys, values = k[:, head].double().clone(), v[:, head].double().clone()
+            if drop:
+                keys[2], values[2] = 0.0, 0.0
+            if kind == "wkv":
+                out[:, head], _ = plain.wkv_scan(q[:, head].double(), keys, values, w[:, head], u[head].double(), torch.zeros((dim, vdim), dtype=F64))
+            else:
+                out[:, head], _ = plain.delta_rule_scan(q[:, head].double(), keys, values, beta[:, head], g[:, head], torch.zeros((dim, vdim), dtype=F64))
+        return (plain.rms_divide(out, eps) * weight.double().view(-1, vdim)[-1:] * plain.silu(gate.double()).view(total, heads, vdim)).reshape(total, -1)
+
+    want, without = plain_run(False), plain_run(True)
+    assert (want[-1] - without[-1]).abs().max() > 0.5
+    state = torch.zeros((2, heads, dim, vdim), dtype=torch.float32, device=DEVICE)
+    shift = torch.zeros((2, 8), dtype=torch.float32, device=DEVICE)
+    got = []
+    for before, now in portions:
+        rows = slice(before, before + now)
+        batch = _batch([(before, now)], [1])
+        if kind == "wkv":
+            rkvg = torch.stack([q[rows].reshape(now, -1), k[rows].reshape(now, -1), v[rows].reshape(now, -1), gate[rows].float()]).to(dtype)
+            got.append(ops.wkv_recurrent(rkvg.contiguous().to(DEVICE), z[rows].to(DEVICE), w0.to(DEVICE), u.to(DEVICE), weight.to(DEVICE),
+                                         state, batch, heads, dim, eps, h=torch.zeros((now, 8), dtype=dtype, device=DEVICE), shift_state=shift))
+        else:
+            pre = torch.cat([q[rows].reshape(now, -1), k[rows].reshape(now, -1), v[rows].reshape(now, -1)], dim=1)
+            got.append(ops.delta_rule_recurrent(gate[rows].contiguous().to(DEVICE), 0, pre.to(DEVICE), wide[rows].to(DEVICE), a_log.to(DEVICE),
+                                                dt_bias.to(DEVICE), weight.to(DEVICE), state, batch, heads, heads, dim, vdim, eps))
+    got = torch.cat(got).cpu().double()
+    tolerance = 2e-4 if dtype == torch.float32 else 2e-2
+    assert torch.allclose(got, want, atol=tolerance, rtol=tolerance)
+
+
+def _windowed_attention_case(dtype, heads, kv_heads, dim, vdim, lengths, new_tokens, page_size, window, seed, spike):
+    """Queries (rotated and normalised already), paged keys and values on shuffled pages, and softmax attention over the
+    last ``window`` keys of every query in float64.  ``spike`` = (query index, key position): that query and that key are
+    made parallel and long, so that their score towers over the row's other scores."""
+    generator = torch.Generator().manual_seed(seed)
+    queries = [(s, p) for s, (length, count) in enumerate(zip(lengths, new_tokens)) for p in range(length - count, length)]
+    keys = [torch.randn((length, kv_heads, dim), generator=generator).to(dtype) for length in lengths]
+    values = [torch.randn((length, kv_heads, vdim), generator=generator).to(dtype) for length in lengths]
+    q = torch.randn((len(queries), heads, dim), generator=generator).to(dtype)
+    scale = 1.3 / math.sqrt(dim)
+    if spike is not None:
+        index, position = spike
+        direction = torch.nn.functional.normalize(torch.randn((dim,), generator=generator), dim=0)
+        size = math.sqrt(30.0 / scale)
+        keys[queries[index][0]][position] = (direction * size).to(dtype)
+        q[index] = (direction * size).to(dtype)
+    blocks = [-(-length // page_size) for length in lengths]
+    order = torch.randperm(sum(blocks), generator=generator).tolist()
+    tables = torch.zeros((len(lengths), max(blocks)), dtype=torch.int32)
+    k_pages = torch.zeros((sum(blocks), kv_heads, page_size, dim), dtype=dtype)
+    v_pages = torch.zeros((sum(blocks), kv_heads, page_size, vdim), dtype=dtype)
+    for s, length in enumerate(lengths):
+        for block in range(blocks[s]):
+            page = order.pop()
+            tables[s, block] = page
+            rows = slice(block * page_size, min(length, (block + 1) * page_size))
+            k_pages[page, :, :rows.stop - rows.start] = keys[s][rows].transpose(0, 1)
+            v_pages[page, :, :rows.stop - rows.start] = values[s][rows].transpose(0, 1)
+    want = torch.zeros((len(queries), heads, vdim), dtype=F64)
+    spike_weight = None
+    for index, (s, p) in enumerate(queries):
+        first = max(0, p - window + 1)
+        for head in range(heads):
+            group = head // (heads // kv_heads)
+            weights = torch.softmax((keys[s][first:p + 1, group].double() @ q[index, head].double()) * scale, dim=0)
+            want[index, head] = weights @ values[s][first:p + 1, group].double()
+            if spike is not None and index == spike[0] and spike[1] >= first:
+                spike_weight = float(weights[spike[1] - first]) if spike_weight is None else min(spike_weight, float(weights[spike[1] - first]))
+    return queries, q, k_pages, v_pages, tables, blocks, scale, want.reshape(len(queries), heads * vdim), spike_weight
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim,window,page_size", [(4, 2, 128, 128, 100, 16), (6, 2, 64, 64, 33, 8), (4, 1, 32, 48, 64, 16),
+                                                                      (8, 2, 128, 128, 1, 16), (3, 3, 24, 24, 1000, 4)])
+def test_window_edges_in_prompts_and_decoding(dtype, heads, kv_heads, dim, vdim, window, page_size):
+    """Attention as a step runs it (a whole prompt, a portion behind cached tokens, single decoded tokens, one of them at
+    the end of a long context), with one score that towers over its row: for the key that has just come into the window
+    of a decoded token and of a prompt row (it must carry the row), for the key that has just left it (it must not be
+    seen, whatever its score), for a key in the middle of the window, and for the last slot of a page."""
+    from llmserver_b200 import ops
+    from llmserver_b200.engine.batch import SequenceSlice, build_batch
+    from llmserver_b200.ops.library import check_wait_errors
+    lengths = [300, 41, 1, 130, 700]
+    new_tokens = [1, 41, 1, 30, 1]
+    counts = [sum(new_tokens[:s]) for s in range(len(lengths))]
+    decoded, prompt_row = counts[4], counts[3] + 20          # the query at position 699; a prompt row at position 120
+    spikes = [None]
+    for index, position in ((decoded, 699), (prompt_row, 120)):
+        inside = position - window + 1
+        if inside >= 0:
+            spikes += [(index, inside), (index, max(inside, (position + inside) // 2))]
+        if inside >= 1:
+            spikes.append((index, inside - 1))
+        if window > position:
+            spikes.append((index, 2))                        # a key hundreds of tokens back, near the sequence's start
+    spikes.append((decoded, 699 - (699 % page_size) - 1))     # the last slot of a page, inside the window or not
+    for spike in spikes:
+        queries, q, k_pages, v_pages, tables, blocks, scale, want, spike_weight = _windowed_attention_case(
+            dtype, heads, kv_heads, dim, vdim, lengths, new_tokens, page_size, window, 37, spike)
+        slices = [SequenceSlice(f"r{s}", [0] * count, length - count, [], [tables[s, :blocks[s]].tolist()], 0)
+                  for s, (length, count) in enumerate(zip(lengths, new_tokens))]
+        batch = build_batch(slices, 1, DEVICE)
+        packed = torch.zeros((len(queries), (heads + kv_heads) * dim + kv_heads * vdim), dtype=dtype)
+        packed[:, :heads * dim] = q.reshape(len(queries), heads * dim)
+        out = ops.attention(packed.to(DEVICE), batch, batch.block_tables[0], k_pages.to(DEVICE), v_pages.to(DEVICE), heads, kv_heads,
+                            dim, scale, window=window, value_dim=vdim, precise=True)
+        torch.cuda.synchronize()
+        check_wait_errors()
+        error = (out.cpu().double() - want).abs().max(dim=-1).values / want.abs().max(dim=-1).values.clamp_min(0.05)
+        allowed = 2e-5 if dtype == torch.float32 else 6e-3
+        assert error.max() < allowed, f"spike {spike}: row {int(error.argmax())} of {len(queries)} differs by {float(error.max()):.2e}"
+        if spike_weight is not None:
+            assert spike_weight > 0.9       # a kernel that missed the key would be far off
+
+
 # ------------------------------------------------------------------------------------------------ whole models
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", NAMES)
