@@ -453,9 +453,9 @@ def _vibepel_mixers(width, heads, kv_heads):
     """Mixers of one width: attention with heads of 128 over a window of 1024 tokens, half of each head rotating, beside a
     gated delta rule with half as many heads of 128 x 128; time mixing with heads of 64 channels across the stream."""
     left = dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, scale=128 ** -0.5, mask={"size": 1024},
-                rot={"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}})
+                rot={"base": 500000.0, "dims": 64, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 8192}})
     right = dict(heads=heads // 2, kv_heads=kv_heads, dim=128, vdim=128, conv=4)
-    return (dict(left=left, right=right, left_scale=0.6, right_scale=0.5), dict(heads=width // 64, dim=64, w_rank=64))
+    return (dict(left=left, right=right, left_scale=0.7, right_scale=0.4), dict(heads=width // 64, dim=64, w_rank=64))
 
 
 # Layer sizes that resemble served models: four layers of one kind of mixer, or parallel, time mixing, parallel,

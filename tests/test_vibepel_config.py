@@ -70,7 +70,7 @@ def test_specification_parts_and_constants():
     assert len(spec.positions) == 3 and spec.layers[0].position is None
     assert {spec.positions[layer.position].kind for layer in spec.layers if layer.position} == {"banded_rotary", "rotary"}
     branches = spec.layers[1].mixer.get("branches")
-    assert [(name, scale) for name, _, scale, _ in branches] == [("left", 0.6), ("right", 0.5)]
+    assert [(name, scale) for name, _, scale, _ in branches] == [("left", 0.62), ("right", 0.48)]
     assert branches[0][1].get("window") == 23 and branches[0][1].get("qk_norm") and branches[1][1].get("conv") == 4
 
 

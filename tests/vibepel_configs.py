@@ -51,11 +51,11 @@ BOTH_KINDS = {
     "architecture": "Vibepel", "vocab": 300, "width": 96, "norm": {"eps": 1e-6}, "embedding": {"scale": 2.5}, "logit_softcap": 25.0,
     "layers": [
         _wkv(3, 16, 12, _dense(64)),
-        _parallel(_left(4, 2, 16, 16, 0.25, 23, 16, base=1e6, scaling={"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64}),
-                  _right(4, 2, 16, 24, 4), 0.6, 0.5, _dense(80)),
+        _parallel(_left(4, 2, 16, 16, 0.25, 23, 16, base=1e6, scaling={"factor": 6.0, "low": 1.0, "high": 3.5, "original": 64}),
+                  _right(4, 2, 16, 24, 4), 0.62, 0.48, _dense(80)),
         _wkv(6, 16, 20, None),
         _parallel(_left(2, 1, 32, 48, 0.18, 9, 10), _right(2, 2, 32, 16, 3), 0.8, 1.2, None),
-        _parallel(_left(4, 2, 16, 16, 0.25, 23, 16, base=1e6), _right(4, 2, 16, 24, 2), 0.6, 0.5, _dense(80)),
+        _parallel(_left(4, 2, 16, 16, 0.25, 23, 16, base=1e6), _right(4, 2, 16, 24, 2), 0.58, 0.52, _dense(80)),
     ],
 }
 
@@ -63,7 +63,7 @@ BOTH_KINDS = {
 TENSOR_CORE_SIZES = {
     "architecture": "Vibepel", "vocab": 384, "width": 192, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "logit_softcap": 30.0,
     "layers": [
-        _parallel(_left(4, 2, 64, 64, 0.125, 70, 32, base=1e5, scaling={"factor": 8.0, "low": 1.0, "high": 4.0, "original": 128}),
+        _parallel(_left(4, 2, 64, 64, 0.125, 70, 32, base=1e5, scaling={"factor": 5.0, "low": 0.5, "high": 4.0, "original": 128}),
                   _right(4, 2, 64, 64, 4), 0.7, 0.4, _dense(256)),
         _wkv(3, 64, 32, _dense(128)),
         _parallel(_left(2, 1, 128, 128, 0.09, 150, 128, base=1e4), _right(2, 1, 128, 128, 4), 0.5, 0.5, None),
