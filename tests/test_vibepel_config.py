@@ -215,3 +215,34 @@ def test_plain_forward_runs_every_configuration():
         # causal: a later token changes no earlier row
         changed = plain.forward(raw, weights, tokens[:-1] + [(tokens[-1] + 1) % raw["vocab"]])
         assert torch.allclose(changed[:-1], logits[:-1], atol=1e-12) and not torch.allclose(changed[-1], logits[-1], atol=1e-9)
+
+
+def test_segments_of_long_portions_are_chosen_by_length_type_and_scratch():
+    """The recurrences walk a long bfloat16 portion by segments of at least 64 tokens, at most 64 of them, within a bound
+    on the scratch (a state and a transition per sequence, segment and head); short steps, 32-bit steps and steps whose
+    scratch would not hold two segments run in one pass; a given segment length is taken as it is."""
+    from types import SimpleNamespace
+
+    from llmserver_b200 import ops
+
+    def choose(n_seqs, longest, dtype, segment=None, heads=2, dim=16, vdim=16, move=16):
+        batch = SimpleNamespace(n_seqs=n_seqs, max_q_len=longest, scratch={})
+        chosen = ops._recurrence_segments(batch, torch.empty((1,), dtype=dtype), segment, heads, dim, vdim, move)
+        return chosen, batch
+
+    (segment, segments, state, move), batch = choose(1, 2048, torch.bfloat16)
+    assert (segment, segments) == (64, 32) and state.shape == (1, 32, 2, 16, 16) and move.shape == (1, 32, 2, 16, 16)
+    assert len(batch.scratch) == 1
+    assert choose(1, 2048, torch.float32)[0] == (0, 0, None, None)
+    assert choose(3, 127, torch.bfloat16)[0] == (0, 0, None, None)
+    assert choose(3, 128, torch.bfloat16)[0][:2] == (64, 2)
+    assert choose(1, 64 * 64 + 1, torch.bfloat16)[0][:2] == (65, 64)            # no more than 64 segments
+    assert choose(2, 100, torch.bfloat16, segment=7)[0][:2] == (7, 15)
+    assert choose(2, 100, torch.float32, segment=7)[0][:2] == (7, 15)
+    # a diagonal transition takes one value per key channel
+    assert choose(1, 300, torch.bfloat16, move=1)[0][3].shape == (1, 5, 2, 16, 1)
+    # heads of 128 x 128 with full transitions: 128 KiB per (sequence, segment, head); 16 heads and 100 sequences leave
+    # room for 5 segments of a 2048-token portion, 600 sequences for none
+    many = choose(100, 2048, torch.bfloat16, heads=16, dim=128, vdim=128, move=128)[0]
+    assert many[:2] == (410, 5) and many[2].numel() * 4 + many[3].numel() * 4 <= ops.REC_SCRATCH_BYTES
+    assert choose(600, 2048, torch.bfloat16, heads=16, dim=128, vdim=128, move=128)[0] == (0, 0, None, None)
