@@ -5,7 +5,8 @@ from .qwen3 import Qwen3Config, FULL_ATTENTION, SLIDING_ATTENTION
 from .gefarax import GefaraxConfig
 from .dikusun import DikusunConfig
 from .vibepel import VibepelConfig
+from .zeridra import ZeridraConfig
 
 __all__ = ["UnsupportedModelError", "WeightLoadError", "PartSpec", "LayerSpec", "ScheduleEntry", "ModelSpec",
            "ARCHITECTURES", "Architecture", "register_architecture", "architecture_of", "read_config",
-           "Qwen3Config", "GefaraxConfig", "DikusunConfig", "VibepelConfig", "FULL_ATTENTION", "SLIDING_ATTENTION"]
+           "Qwen3Config", "GefaraxConfig", "DikusunConfig", "VibepelConfig", "ZeridraConfig", "FULL_ATTENTION", "SLIDING_ATTENTION"]

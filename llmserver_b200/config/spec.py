@@ -85,6 +85,7 @@ class ModelSpec:
     head_name: str = "lm_head.weight"
     tie_head: bool = False
     embedding_scale: float = 1.0    # the embedded tokens are multiplied by this as they enter the stream
+    logit_scale: float = 1.0        # the head's products are multiplied by this (before the cap)
     logit_softcap: float = 0.0      # c > 0: the logits leave as c * tanh(logits / c)
     max_positions: Optional[int] = None
     eos_token_ids: Tuple[int, ...] = ()

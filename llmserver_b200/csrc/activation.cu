@@ -96,7 +96,7 @@ LLM_EXPORT int llm_silu_mul(const void* gate_up, void* out, int n_rows, int inte
 // Point-wise steps that stand alone (32-bit arithmetic, one rounding on the store):
 //   kind 0  out = max(x, 0)^2                                the activation of a feed-forward without a gate
 //   kind 1  out = tanh(x), x given in 32-bit                 a low-rank projection's activation, narrowed once
-//   kind 2  out = a * tanh(x / a), 32-bit and in place       capped logits
+//   kind 2  out = a * tanh(b * x / a), 32-bit and in place   logits scaled by b, then capped
 //   kind 3  out = a * x + b * y                              two branches' outputs joined
 // Eight elements per thread and turn through 16-byte accesses where count and pointers allow, else one by one.
 enum : int { POINT_RELU_SQUARED = 0, POINT_TANH = 1, POINT_SOFTCAP = 2, POINT_SCALED_SUM = 3 };
@@ -105,7 +105,7 @@ template <int KIND>
 __device__ __forceinline__ float pointwise_value(float x, float y, float a, float b) {
     if (KIND == POINT_RELU_SQUARED) { const float r = fmaxf(x, 0.0f); return r * r; }
     if (KIND == POINT_TANH) return tanhf(x);
-    if (KIND == POINT_SOFTCAP) return a * tanhf(x / a);
+    if (KIND == POINT_SOFTCAP) return a * tanhf(x * b / a);
     return a * x + b * y;
 }
 

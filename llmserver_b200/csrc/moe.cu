@@ -8,8 +8,10 @@
 //   linear     matrix.  One warp per output element, its sum taken over k in an order that depends on the inner size
 //              alone, so a pair's result does not depend on what else the step holds.  As a gated form the matrix
 //              holds gate rows then up rows and the output is the expert's activation
-//                  g = min(gate, limit), u = clamp(up, -limit, limit), y = g * sigmoid(alpha * g) * (u + 1)
-//              computed in 32-bit and rounded once.  Read-once for steps of few tokens; prompts take the tiled
+//                  g = min(gate, limit), u = clamp(up, -limit, limit), y = g * sigmoid(alpha * g) * (u + up_shift)
+//              computed in 32-bit and rounded once (an infinite limit, alpha 1 and up_shift 0 give silu(gate) * up).
+//              With `in_scale` pair p's input row is multiplied by in_scale[p] as it is read (32-bit): a routing
+//              weight that acts on what goes into an expert.  Read-once for steps of few tokens; prompts take the tiled
 //              kernels of moe_grouped.cu.
 //   combine    out[t] = sum_j weight[t, j] * down[t * top + j] (+ shared[t]) in 32-bit, slots in order.
 #include "common.cuh"
@@ -119,22 +121,24 @@ __global__ void moe_select_kernel(const float* __restrict__ logits, const float*
     }
 }
 
-__device__ __forceinline__ float gated_activation(float gate, float up, float limit, float alpha) {
+__device__ __forceinline__ float gated_activation(float gate, float up, float limit, float alpha, float up_shift = 1.0f) {
     const float g = fminf(gate, limit);
     const float u = fminf(fmaxf(up, -limit), limit);
-    return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+    return g / (1.0f + expf(-alpha * g)) * (u + up_shift);
 }
 
 // One warp per (pair, output element).  `rows` output elements per pair; the gated form reads row r and row rows + r.
 template <typename T, typename O, bool GATED>
 __global__ void indexed_linear_kernel(const T* __restrict__ in, const T* __restrict__ weight, const int* __restrict__ index,
-                                      O* __restrict__ out, int rows, int inner, int in_div, float limit, float alpha, int index_mod) {
+                                      O* __restrict__ out, int rows, int inner, int in_div, float limit, float alpha, int index_mod,
+                                      const float* __restrict__ in_scale, float up_shift) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float in_row[];       // [inner]
     const int pair = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const T* src = in + (size_t)(pair / in_div) * inner;
-    for (int i = threadIdx.x; i < inner; i += blockDim.x) in_row[i] = Num<T>::load(src + i);
+    const float row_scale = in_scale ? in_scale[pair] : 1.0f;
+    for (int i = threadIdx.x; i < inner; i += blockDim.x) in_row[i] = Num<T>::load(src + i) * row_scale;
     __syncthreads();
     const int expert = index ? index[pair] : (index_mod > 0 ? pair % index_mod : 0);     // no index: pair p uses matrix p mod index_mod
     const T* matrix = weight + (size_t)expert * (GATED ? 2 : 1) * rows * inner;
@@ -178,7 +182,7 @@ __global__ void indexed_linear_kernel(const T* __restrict__ in, const T* __restr
         const float total = warp_sum(sum[q]);
         const float total_up = GATED ? warp_sum(sum_up[q]) : 0.0f;
         if (lane == 0 && r0 + q < rows) {
-            const float value = GATED ? gated_activation(total, total_up, limit, alpha) : total;
+            const float value = GATED ? gated_activation(total, total_up, limit, alpha, up_shift) : total;
             Num<O>::store(out + (size_t)pair * rows + r0 + q, value);
         }
     }
@@ -287,7 +291,7 @@ LLM_EXPORT int llm_moe_select(const float* logits, const float* correction, int*
 
 LLM_EXPORT int llm_indexed_linear(const void* in, const void* weight, const int* index, void* out, int n_pairs, int rows,
                                   int inner, int in_div, int gated, float limit, float alpha, int dtype, int out_f32,
-                                  int index_mod, cudaStream_t stream) {
+                                  int index_mod, const float* in_scale, float up_shift, cudaStream_t stream) {
     if (n_pairs == 0 || rows == 0) return LLM_OK;
     if (in_div <= 0 || inner <= 0) {
         llm_set_error("indexed_linear: in_div %d and inner %d must be positive", in_div, inner);
@@ -311,7 +315,7 @@ LLM_EXPORT int llm_indexed_linear(const void* in, const void* weight, const int*
             if (status != LLM_OK) return status;                                                                        \
         }                                                                                                               \
         llm_launch(indexed_linear_kernel<T, O, GATED>, grid, warps * 32, shared, stream, (const T*)in, (const T*)weight, index, \
-                   (O*)out, rows, inner, in_div, limit, alpha, index_mod);                                                       \
+                   (O*)out, rows, inner, in_div, limit, alpha, index_mod, in_scale, up_shift);                                  \
     } while (0)
     LLM_DISPATCH_DTYPE(dtype, {
         if (gated && out_f32) {

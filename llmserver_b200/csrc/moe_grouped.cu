@@ -88,7 +88,7 @@ template <bool GATED>
 __global__ void __launch_bounds__(kGemmThreads) moe_grouped_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w,
                                                                    const int* __restrict__ tiles, const int* __restrict__ pair_of_row,
                                                                    int in_div, void* __restrict__ out, int out_cols, int inner,
-                                                                   float limit, float alpha) {
+                                                                   float limit, float alpha, float up_shift) {
     pdl_trigger();
     pdl_wait();
     if ((int)blockIdx.x >= tiles[0]) return;
@@ -204,7 +204,7 @@ __global__ void __launch_bounds__(kGemmThreads) moe_grouped_kernel(const __nv_bf
                     for (int v = 0; v < 2; ++v) {
                         const float gate = fminf(acc[i][2 * j][2 * half + v], limit);
                         const float up = fminf(fmaxf(acc[i][2 * j + 1][2 * half + v], -limit), limit);
-                        y[v] = gate / (1.0f + __expf(-alpha * gate)) * (up + 1.0f);
+                        y[v] = gate / (1.0f + __expf(-alpha * gate)) * (up + up_shift);
                     }
                     if (feature + 1 < out_cols) {
                         *reinterpret_cast<__nv_bfloat162*>(dst + feature) = __floats2bfloat162_rn(y[0], y[1]);
@@ -281,7 +281,7 @@ LLM_EXPORT int llm_moe_grouped_supports(int out_cols, int inner, int gated) {
 // inner]; pair_of_row null: row r of the plan reads row r of a, else row pair_of_row[r] / in_div; out: bfloat16
 // [n_pairs, out_cols] (gated) or float32 [n_pairs, out_cols], rows in the plan's order.
 LLM_EXPORT int llm_moe_grouped(const void* a, const void* w, const int* tiles, const int* pair_of_row, int in_div, void* out,
-                               int out_cols, int inner, int max_tiles, int gated, float limit, float alpha, cudaStream_t stream) {
+                               int out_cols, int inner, int max_tiles, int gated, float limit, float alpha, float up_shift, cudaStream_t stream) {
     if (max_tiles <= 0) return LLM_OK;
     if (!llm_moe_grouped_supports(out_cols, inner, gated) || in_div <= 0) {
         llm_set_error("moe_grouped: %d output columns over an inner size of %d are not supported (inner a multiple of %d, "
@@ -298,11 +298,11 @@ LLM_EXPORT int llm_moe_grouped(const void* a, const void* w, const int* tiles, c
     if (gated) {
         if (int status = llm_raise_shared_limit((const void*)moe_grouped_kernel<true>, shared, "moe_grouped")) return status;
         llm_launch(moe_grouped_kernel<true>, grid, kGemmThreads, shared, stream, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w,
-                   tiles, pair_of_row, in_div, out, out_cols, inner, limit, alpha);
+                   tiles, pair_of_row, in_div, out, out_cols, inner, limit, alpha, up_shift);
     } else {
         if (int status = llm_raise_shared_limit((const void*)moe_grouped_kernel<false>, shared, "moe_grouped")) return status;
         llm_launch(moe_grouped_kernel<false>, grid, kGemmThreads, shared, stream, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w,
-                   tiles, pair_of_row, in_div, out, out_cols, inner, limit, alpha);
+                   tiles, pair_of_row, in_div, out, out_cols, inner, limit, alpha, up_shift);
     }
     return llm_check_launch("moe_grouped");
 }

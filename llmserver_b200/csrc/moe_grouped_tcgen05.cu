@@ -34,7 +34,7 @@ __global__ void __launch_bounds__(kTcThreads) moe_grouped_tc_kernel(const __grid
                                                                     const __grid_constant__ CUtensorMap map_w,
                                                                     const int* __restrict__ tiles, void* __restrict__ out, int out_cols,
                                                                     int col_tiles, int inner, float limit, float alpha,
-                                                                    int* __restrict__ error_flag) {
+                                                                    float up_shift, int* __restrict__ error_flag) {
     pdl_trigger();
     pdl_wait();
     const int total = tiles[0] * col_tiles;      // (row tile, column tile) pairs; block b takes b, b + gridDim.x, ...
@@ -156,7 +156,7 @@ __global__ void __launch_bounds__(kTcThreads) moe_grouped_tc_kernel(const __grid
                             for (int h = 0; h < 2; ++h) {
                                 const float g = fminf(__uint_as_float(gate[v + e + h]), limit);
                                 const float u = fminf(fmaxf(__uint_as_float(up[v + e + h]), -limit), limit);
-                                y[h] = g / (1.0f + __expf(-alpha * g)) * (u + 1.0f);
+                                y[h] = g / (1.0f + __expf(-alpha * g)) * (u + up_shift);
                             }
                             packed[e / 2] = tc5::pack2(y[0], y[1]);
                         }
@@ -193,12 +193,27 @@ __global__ void __launch_bounds__(kTcThreads) moe_grouped_tc_kernel(const __grid
 }
 
 // out[r] = x[pair_of_row[r] / in_div]: the tokens' rows in the plan's order, for a product that reads its rows by TMA.
+// With `pair_scale` the row of pair p is multiplied by pair_scale[p] on the way (32-bit product, one rounding): a routing
+// weight that acts on what goes into an expert.
 __global__ void moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ pair_of_row, int in_div,
-                                       __nv_bfloat16* __restrict__ out, int width) {
+                                       __nv_bfloat16* __restrict__ out, int width, const float* __restrict__ pair_scale) {
     pdl_trigger();
     pdl_wait();
     const size_t row = blockIdx.x;
-    const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(pair_of_row[row] / in_div) * width);
+    const int pair = pair_of_row[row];
+    const __nv_bfloat16* from = x + (size_t)(pair / in_div) * width;
+    if (pair_scale) {
+        const float scale = pair_scale[pair];
+        for (int i = threadIdx.x; i < width / 8; i += blockDim.x) {
+            float values[8];
+            load8<__nv_bfloat16>(from + i * 8, values);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) values[j] *= scale;
+            store8<__nv_bfloat16>(out + row * width + i * 8, values);
+        }
+        return;
+    }
+    const uint4* src = reinterpret_cast<const uint4*>(from);
     uint4* dst = reinterpret_cast<uint4*>(out + row * width);
     for (int i = threadIdx.x; i < width / 8; i += blockDim.x) dst[i] = src[i];
 }
@@ -210,20 +225,22 @@ LLM_EXPORT int llm_moe_grouped_tc_supports(int out_cols, int inner, int gated) {
 }
 
 LLM_EXPORT int llm_moe_gather_rows(const void* x, const int* pair_of_row, int in_div, void* out, int n_rows, int width,
-                                   cudaStream_t stream) {
+                                   const float* pair_scale, cudaStream_t stream) {
     if (n_rows == 0) return LLM_OK;
     if (width % 8 || !aligned16(x) || !aligned16(out) || in_div <= 0) {
         llm_set_error("moe_gather_rows: rows of %d elements must be a multiple of 8 and 16-byte aligned", width);
         return LLM_REFUSED;
     }
-    llm_launch(moe_gather_rows_kernel, n_rows, 128, 0, stream, (const __nv_bfloat16*)x, pair_of_row, in_div, (__nv_bfloat16*)out, width);
+    llm_launch(moe_gather_rows_kernel, n_rows, 128, 0, stream, (const __nv_bfloat16*)x, pair_of_row, in_div, (__nv_bfloat16*)out, width,
+               pair_scale);
     return llm_check_launch("moe_gather_rows");
 }
 
 // a: bfloat16 [n_rows, inner] in the plan's order; w: bfloat16 [experts, (gated ? 2 : 1) * out_cols, inner]; out: bfloat16
 // [n_rows, out_cols] (gated) or float32 [n_rows, out_cols].
 LLM_EXPORT int llm_moe_grouped_tc(const void* a, int n_rows, const void* w, int experts, const int* tiles, void* out, int out_cols,
-                                  int inner, int max_tiles, int gated, float limit, float alpha, int* error_flag, cudaStream_t stream) {
+                                  int inner, int max_tiles, int gated, float limit, float alpha, float up_shift, int* error_flag,
+                                  cudaStream_t stream) {
     if (max_tiles <= 0 || n_rows <= 0) return LLM_OK;
     if (!llm_moe_grouped_tc_supports(out_cols, inner, gated) || !aligned16(a) || !aligned16(w) || !aligned16(out)) {
         llm_set_error("moe_grouped_tc: %d output columns over an inner size of %d are not supported (both multiples of 8, "
@@ -249,11 +266,11 @@ LLM_EXPORT int llm_moe_grouped_tc(const void* a, int n_rows, const void* w, int 
     if (gated) {
         if (int status = llm_raise_shared_limit((const void*)moe_grouped_tc_kernel<true>, shared, "moe_grouped_tc")) return status;
         llm_launch(moe_grouped_tc_kernel<true>, blocks, kTcThreads, shared, stream, map_a, map_w, tiles, out, out_cols, col_tiles, inner,
-                   limit, alpha, error_flag);
+                   limit, alpha, up_shift, error_flag);
     } else {
         if (int status = llm_raise_shared_limit((const void*)moe_grouped_tc_kernel<false>, shared, "moe_grouped_tc")) return status;
         llm_launch(moe_grouped_tc_kernel<false>, blocks, kTcThreads, shared, stream, map_a, map_w, tiles, out, out_cols, col_tiles, inner,
-                   limit, alpha, error_flag);
+                   limit, alpha, up_shift, error_flag);
     }
     return llm_check_launch("moe_grouped_tc");
 }

@@ -331,3 +331,127 @@ LLM_EXPORT int llm_normed_add_rmsnorm(float* residual, const void* delta, const 
     });
     return llm_check_launch("normed_add_rmsnorm");
 }
+
+// Two sub-layers that read the same normalised stream and join it together, each through a learned scale per channel,
+// fused with the norm that follows:
+//   residual[r] += a[r] * scale_a (+ b[r] * scale_b)        (32-bit products and sums; scales are 32-bit [width])
+//   out[o]       = residual[r] * rsqrt(mean(residual[r]^2) + eps) * weight          (skipped when out is null)
+// `b` may be absent (a layer without its second sub-layer).  With `rows` the stream is left as it was.
+template <typename T, typename W>
+__global__ void scaled_add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ a, const float* __restrict__ scale_a,
+                                          const T* __restrict__ b, const float* __restrict__ scale_b, const W* __restrict__ weight,
+                                          T* __restrict__ out, const int* __restrict__ rows, int width, float eps, int write_residual) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float scratch[33];
+    extern __shared__ float updated[];     // [width]
+    const int o = blockIdx.x;
+    const int r = rows ? rows[o] : o;
+    float* res = residual + (size_t)r * width;
+    float sum_squares = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = res[i];
+        float added = Num<T>::load(a + (size_t)r * width + i) * scale_a[i];
+        if (b) added = fmaf(Num<T>::load(b + (size_t)r * width + i), scale_b[i], added);
+        v += added;
+        if (write_residual) res[i] = v;
+        updated[i] = v;
+        sum_squares += v * v;
+    }
+    if (!out) return;
+    const float inverse = rsqrtf(block_sum(sum_squares, scratch) / (float)width + eps);
+    T* dst = out + (size_t)o * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        Num<T>::store(dst + i, updated[i] * inverse * Num<W>::load(weight + i));
+}
+
+// The same with 16-byte accesses and the row held in registers between the passes; sums in the scalar form's order per
+// element, the sum of squares in an order that depends on the width only.
+template <typename T, typename W>
+__global__ void scaled_add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ a, const float* __restrict__ scale_a,
+                                              const T* __restrict__ b, const float* __restrict__ scale_b, const W* __restrict__ weight,
+                                              T* __restrict__ out, const int* __restrict__ rows, int width, float eps,
+                                              int write_residual) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const int o = blockIdx.x;
+    const int r = rows ? rows[o] : o;
+    float* res = residual + (size_t)r * width;
+    const int chunks = width / kChunk;
+    float values[kMaxChunks][kChunk];
+    float sum_squares = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kMaxChunks; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < chunks) {
+            float part[kChunk], scale[kChunk], added[kChunk];
+            load8<float>(res + c * kChunk, values[i]);
+            load8<T>(a + (size_t)r * width + c * kChunk, part);
+            load8<float>(scale_a + c * kChunk, scale);
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j) added[j] = part[j] * scale[j];
+            if (b) {
+                load8<T>(b + (size_t)r * width + c * kChunk, part);
+                load8<float>(scale_b + c * kChunk, scale);
+#pragma unroll
+                for (int j = 0; j < kChunk; ++j) added[j] = fmaf(part[j], scale[j], added[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j) {
+                values[i][j] += added[j];
+                sum_squares += values[i][j] * values[i][j];
+            }
+            if (write_residual) store8<float>(res + c * kChunk, values[i]);
+        }
+    }
+    if (!out) return;
+    const float inverse = rsqrtf(block_sum(sum_squares, scratch) / (float)width + eps);
+    T* dst = out + (size_t)o * width;
+#pragma unroll
+    for (int i = 0; i < kMaxChunks; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < chunks) {
+            float scale[kChunk], scaled[kChunk];
+            load8<W>(weight + c * kChunk, scale);
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j) scaled[j] = values[i][j] * inverse * scale[j];
+            store8<T>(dst + c * kChunk, scaled);
+        }
+    }
+}
+
+LLM_EXPORT int llm_scaled_add_rmsnorm(float* residual, const void* a, const float* scale_a, const void* b, const float* scale_b,
+                                      const void* weight, void* out, const int* rows, int n_rows, int width, float eps,
+                                      int write_residual, int dtype, int weight_dtype, cudaStream_t stream) {
+    if (n_rows == 0) return LLM_OK;
+    if (!a || !scale_a || (b && !scale_b) || (out && !weight)) {
+        llm_set_error("scaled_add_rmsnorm: a sub-layer output needs its scale, an output the norm's weight");
+        return LLM_REFUSED;
+    }
+    const int chunks = width / kChunk;
+    int threads = ((chunks + 31) / 32) * 32;      // depends on the width only
+    if (threads > 512) threads = 512;
+    const bool vector_form = width % kChunk == 0 && width >= kChunk && chunks <= threads * kMaxChunks && aligned16(residual) &&
+                             aligned16(a) && aligned16(b) && aligned16(scale_a) && aligned16(scale_b) && aligned16(weight) && aligned16(out);
+    if (vector_form) {
+        LLM_DISPATCH_DTYPE_WEIGHT(dtype, weight_dtype,
+                                  (llm_launch(scaled_add_rmsnorm_vec_kernel<T, W>, n_rows, threads, 0, stream, residual, (const T*)a,
+                                      scale_a, (const T*)b, scale_b, (const W*)weight, (T*)out, rows, width, eps, write_residual)));
+        return llm_check_launch("scaled_add_rmsnorm");
+    }
+    const size_t shared = (size_t)width * sizeof(float);
+    if (shared > 200 * 1024) {
+        llm_set_error("scaled_add_rmsnorm: a width of %d needs %zu bytes of shared memory", width, shared);
+        return LLM_REFUSED;
+    }
+    LLM_DISPATCH_DTYPE_WEIGHT(dtype, weight_dtype, {
+        if (shared > 40 * 1024) {
+            const int status = llm_raise_shared_limit((const void*)scaled_add_rmsnorm_kernel<T, W>, shared + 256, "scaled_add_rmsnorm");
+            if (status != LLM_OK) return status;
+        }
+        llm_launch(scaled_add_rmsnorm_kernel<T, W>, n_rows, norm_threads(width), shared, stream, residual, (const T*)a, scale_a,
+                   (const T*)b, scale_b, (const W*)weight, (T*)out, rows, width, eps, write_residual);
+    });
+    return llm_check_launch("scaled_add_rmsnorm");
+}

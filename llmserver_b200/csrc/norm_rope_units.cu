@@ -5,8 +5,13 @@
 // head consists of M units ("maps": a head that attends with several score maps has one query and one key unit per
 // map; M = 1 is the ordinary head).  Columns behind the values are left alone.  One warp per (token, unit):
 //   1. the unit's elements, plus the projection's bias where there is one, in 32-bit;
-//   2. RMSNorm over the unit with a weight shared by all units of its kind (`q_weight` [Dq], `k_weight` [Dk]);
-//   3. the first `rotary_dim` elements rotated, element i paired with i + rotary_dim / 2:
+//   2. RMSNorm over the unit with a weight shared by all units of its kind (`q_weight` [Dq], `k_weight` [Dk]); with
+//      `k_norm_dim` > 0 only the first `k_norm_dim` elements of a key unit are normalised (among themselves) and the
+//      rest stays as projected: a latent with a positional part behind it;
+//   2b. query units multiplied by a factor that grows with the position p,
+//        1 + temp_coef * ln(floor((p + 1) / temp_every) + 1)                      (temp_every 0: no factor);
+//   3. `rotary_dim` elements rotated, from element `q_rot_start` / `k_rot_start` of the unit on (negative: units of
+//      that kind do not rotate), element i paired with i + rotary_dim / 2 or, `interleaved`, 2i with 2i + 1:
 //        (u, v) -> (u cos a - v sin a, v cos a + u sin a),  a = position * inv_freq[i];
 //   4. query units written back where they lie, or packed into `q_out` [N, Hq * M * Dq]; key units written into
 //      the token's slot of the K pages [page, Hkv, slot, M * Dk]; value heads (bias added) into the V pages
@@ -23,7 +28,8 @@ __global__ void norm_rope_units_kernel(T* __restrict__ qkv, int row_width, const
                                        int max_blocks, T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages,
                                        int n_q_heads, int n_kv_heads, int maps, int q_dim, int k_dim, int value_dim,
                                        int page_size, int num_pages, int write_cache, int* __restrict__ error_flag,
-                                       int rotary_dim, int max_dim) {
+                                       int rotary_dim, int max_dim, int k_norm_dim, int q_rot_start, int k_rot_start,
+                                       int interleaved, float temp_coef, int temp_every) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float unit_values[];     // [warps][max_dim]
@@ -77,27 +83,35 @@ __global__ void norm_rope_units_kernel(T* __restrict__ qkv, int row_width, const
                 dst = v_pages + slot * value_dim;
             }
         }
+        const int norm_dim = (is_k && k_norm_dim > 0) ? k_norm_dim : dim;
         float sum_squares = 0.0f;
         for (int i = lane; i < dim; i += 32) {
             float v = Num<T>::load(row + column + i);
             if (bias) v += bias[column + i];
             values[i] = v;
-            sum_squares += v * v;
+            if (i < norm_dim) sum_squares += v * v;
         }
         const W* weight = is_q ? q_weight : (is_k ? k_weight : nullptr);
         if (weight) {
-            const float inverse = rsqrtf(warp_sum(sum_squares) / (float)dim + eps);
-            for (int i = lane; i < dim; i += 32) values[i] = values[i] * inverse * Num<W>::load(weight + i);
+            const float inverse = rsqrtf(warp_sum(sum_squares) / (float)norm_dim + eps);
+            for (int i = lane; i < norm_dim; i += 32) values[i] = values[i] * inverse * Num<W>::load(weight + i);
+        }
+        if (is_q && temp_every > 0) {
+            const float factor = 1.0f + temp_coef * logf((float)((position + 1) / temp_every) + 1.0f);
+            for (int i = lane; i < dim; i += 32) values[i] *= factor;
         }
         __syncwarp();
-        const int turning = (inv_freq && (is_q || is_k)) ? rotary_dim : 0;
+        const int rot_start = is_q ? q_rot_start : (is_k ? k_rot_start : -1);
+        const int turning = (inv_freq && rot_start >= 0) ? rotary_dim : 0;
         for (int i = lane; i < turning / 2; i += 32) {
             const float c = rotation[i].x, s = rotation[i].y;
-            const float u = values[i], v = values[half + i];
-            Num<T>::store(dst + i, u * c - v * s);
-            Num<T>::store(dst + half + i, v * c + u * s);
+            const int first = rot_start + (interleaved ? 2 * i : i), second = interleaved ? first + 1 : first + half;
+            const float u = values[first], v = values[second];
+            Num<T>::store(dst + first, u * c - v * s);
+            Num<T>::store(dst + second, v * c + u * s);
         }
-        for (int i = turning + lane; i < dim; i += 32) Num<T>::store(dst + i, values[i]);
+        for (int i = lane; i < dim; i += 32)
+            if (turning == 0 || i < rot_start || i >= rot_start + turning) Num<T>::store(dst + i, values[i]);
         __syncwarp();      // the next unit of this warp overwrites the values
     }
 }
@@ -107,15 +121,29 @@ LLM_EXPORT int llm_norm_rope_units(void* qkv, int row_width, const float* bias, 
                                    const int* block_tables, int max_blocks, void* q_out, void* k_pages, void* v_pages,
                                    int n_tokens, int n_q_heads, int n_kv_heads, int maps, int q_dim, int k_dim, int value_dim,
                                    int page_size, int num_pages, int write_cache, int* error_flag, int rotary_dim, int dtype,
-                                   int weight_dtype, cudaStream_t stream) {
+                                   int weight_dtype, int k_norm_dim, int q_rot_start, int k_rot_start, int interleaved,
+                                   float temp_coef, int temp_every, cudaStream_t stream) {
     if (n_tokens == 0) return LLM_OK;
     if (inv_freq == nullptr) rotary_dim = 0;
-    if (n_q_heads <= 0 || n_kv_heads <= 0 || maps <= 0 || q_dim <= 0 || k_dim <= 0 || value_dim < 0 || page_size <= 0 || num_pages <= 0) {
-        llm_set_error("norm_rope_units: sizes must be positive (value_dim may be 0)");
+    if (n_kv_heads == 0) {      // queries alone: nothing is cached
+        k_dim = k_dim > 0 ? k_dim : 1;
+        page_size = num_pages = 1;
+        value_dim = 0;
+        if (k_rot_start >= 0) k_rot_start = -1;
+    }
+    if (n_q_heads <= 0 || n_kv_heads < 0 || maps <= 0 || q_dim <= 0 || k_dim <= 0 || value_dim < 0 || page_size <= 0 || num_pages <= 0) {
+        llm_set_error("norm_rope_units: sizes must be positive (value_dim and the key heads may be 0)");
         return LLM_REFUSED;
     }
-    if (rotary_dim < 0 || rotary_dim % 2 || rotary_dim > q_dim || rotary_dim > k_dim) {
-        llm_set_error("norm_rope_units: rotary_dim must be even and at most the unit sizes %d and %d, got %d", q_dim, k_dim, rotary_dim);
+    if (rotary_dim < 0 || rotary_dim % 2 || (q_rot_start >= 0 && q_rot_start + rotary_dim > q_dim) ||
+        (k_rot_start >= 0 && k_rot_start + rotary_dim > k_dim)) {
+        llm_set_error("norm_rope_units: %d rotating elements from %d / %d must be an even number inside units of %d and %d",
+                      rotary_dim, q_rot_start, k_rot_start, q_dim, k_dim);
+        return LLM_REFUSED;
+    }
+    if (k_norm_dim < 0 || k_norm_dim > k_dim || temp_every < 0) {
+        llm_set_error("norm_rope_units: a key unit of %d cannot normalise %d elements (or the temperature's period %d is negative)",
+                      k_dim, k_norm_dim, temp_every);
         return LLM_REFUSED;
     }
     const long long used = (long long)(n_q_heads * maps) * q_dim + (long long)(n_kv_heads * maps) * k_dim + (long long)n_kv_heads * value_dim;
@@ -143,7 +171,7 @@ LLM_EXPORT int llm_norm_rope_units(void* qkv, int row_width, const float* bias, 
         llm_launch(norm_rope_units_kernel<T, W>, grid, warps * 32, shared, stream, (T*)qkv, row_width, bias, (const W*)q_weight,
                    (const W*)k_weight, eps, inv_freq, positions, seq_of_token, block_tables, max_blocks, (T*)q_out, (T*)k_pages,
                    (T*)v_pages, n_q_heads, n_kv_heads, maps, q_dim, k_dim, value_dim, page_size, num_pages, write_cache, error_flag,
-                   rotary_dim, max_dim);
+                   rotary_dim, max_dim, k_norm_dim, q_rot_start, k_rot_start, interleaved, temp_coef, temp_every);
     });
     return llm_check_launch("norm_rope_units");
 }

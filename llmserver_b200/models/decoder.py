@@ -38,7 +38,8 @@ class DecoderModel:
                 weights = {local: source.get(prefix + local) for local in cls.declare_weights(part.as_dict())}
                 built[role] = cls(part.as_dict(), weights, runtime)
             built[block_cls.mixer_role(block_params)].attach(self.positions.get(layer.position) if layer.position else None)
-            self.layers.append(block_cls(block_params, built))
+            own = {local: source.get(layer.prefix + local) for local in block_cls.declare_weights(block_params)}
+            self.layers.append(block_cls(block_params, built, own) if own else block_cls(block_params, built))
         norm_cls = NORMS.get(spec.final_norm.kind)
         self.final_norm = norm_cls(spec.final_norm.as_dict(),
                                    {local: source.get(spec.final_norm_prefix + local)
@@ -113,6 +114,6 @@ class DecoderModel:
         # final norm only where logits are wanted (utils/model.py:147-157)
         normed = self.final_norm.add_norm(residual, delta, rows=batch.logit_rows)
         logits = ops.linear(normed, self.head, out_dtype=torch.float32)
-        if self.spec.logit_softcap:
-            ops.softcap_(logits, self.spec.logit_softcap)
+        if self.spec.logit_softcap or self.spec.logit_scale != 1.0:
+            ops.softcap_(logits, self.spec.logit_softcap, self.spec.logit_scale)
         return logits

@@ -17,10 +17,10 @@ from .library import (KernelError, call, check, declare, dtype_code, launch_coun
 from .stream import STREAM_ROWS, RowScaled, StreamSink
 
 __all__ = ["KernelError", "embedding", "add_rmsnorm", "rmsnorm", "silu_mul", "sample", "qk_norm_rope_kv_write",
-           "attention_generic", "rope_kv_write_split", "normed_add_rmsnorm", "moe_route", "moe_select", "indexed_linear", "moe_combine", "moe_plan", "moe_grouped",
+           "attention_generic", "rope_kv_write_split", "normed_add_rmsnorm", "scaled_add_rmsnorm", "moe_route", "moe_select", "indexed_linear", "moe_combine", "moe_plan", "moe_grouped",
            "moe_grouped_supported", "moe_combine_rows", "ExpertPlan",
            "clamped_glu", "gemm_f32", "linear", "linear_wide", "qkv_projection", "gate_up_silu", "interleave_gate_up", "require_device", "library", "launch_count",
-           "RowScaled", "StreamSink", "STREAM_ROWS", "unscaled_rows_supported", "norm_rope_units", "attention_diff", "gla_supported",
+           "RowScaled", "StreamSink", "STREAM_ROWS", "unscaled_rows_supported", "norm_rope_units", "rotate_units", "attention_diff", "gla_supported",
            "gla_recurrent", "head_linear", "relu_squared", "tanh_narrow", "softcap_", "scaled_sum", "token_shift_mix",
            "short_conv_units", "matrix_recurrence_supported", "wkv_recurrent", "delta_rule_recurrent"]
 
@@ -301,27 +301,69 @@ def normed_add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], po
     return out
 
 
+def scaled_add_rmsnorm(residual: torch.Tensor, a: torch.Tensor, scale_a: torch.Tensor, b: Optional[torch.Tensor],
+                       scale_b: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float,
+                       rows: Optional[torch.Tensor] = None, act_dtype: Optional[torch.dtype] = None,
+                       want_output: bool = True) -> Optional[torch.Tensor]:
+    """residual += a * scale_a (+ b * scale_b), 32-bit and in place, the scales float32 [width] per channel; then, unless
+    ``want_output`` is False, returns rmsnorm(residual) * weight in the activation type.  ``a`` and ``b`` are two
+    sub-layers' outputs in the activation type.  With ``rows`` (int32) output row o comes from row rows[o] and the stream
+    is left as it was."""
+    check(residual, "residual", torch.float32)
+    width = residual.shape[-1]
+    act = act_dtype or a.dtype
+    for name, part, scale in (("first output", a, scale_a), ("second output", b, scale_b)):
+        if part is None:
+            continue
+        check(part, name, act, width)
+        if part.shape != residual.shape:
+            raise KernelError(f"the {name} {tuple(part.shape)} does not match the stream {tuple(residual.shape)}")
+        check(scale, name + "'s scale", torch.float32, width)
+    if want_output:
+        check(weight, "norm weight", last_dim=width)
+    if rows is not None:
+        check(rows, "rows", torch.int32)
+        n_rows = rows.numel()
+    else:
+        n_rows = residual.numel() // width
+    out = torch.empty((n_rows, width), dtype=act, device=residual.device) if want_output else None
+    call("llm_scaled_add_rmsnorm", residual.data_ptr(), a.data_ptr(), scale_a.data_ptr(), pointer(b), pointer(scale_b),
+         pointer(weight) if want_output else 0, pointer(out), pointer(rows), n_rows, width, float(eps), int(rows is None),
+         dtype_code(act), dtype_code(weight.dtype if weight is not None else act), stream_handle())
+    return out
+
+
 def norm_rope_units(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, block_tables: torch.Tensor,
                     k_pages: torch.Tensor, v_pages: Optional[torch.Tensor], n_q_heads: int, n_kv_heads: int, maps: int,
                     q_dim: int, k_dim: int, value_dim: int, error_flag: torch.Tensor, bias: Optional[torch.Tensor] = None,
                     q_weight: Optional[torch.Tensor] = None, k_weight: Optional[torch.Tensor] = None, eps: float = 0.0,
                     inv_freq: Optional[torch.Tensor] = None, rotary_dim: int = 0, q_out: Optional[torch.Tensor] = None,
-                    write_cache: bool = True) -> None:
+                    write_cache: bool = True, k_norm_dim: int = 0, q_rot_start: int = 0, k_rot_start: int = 0,
+                    interleaved: bool = False, q_temp: Optional[tuple] = None) -> None:
     """On the packed projection ``qkv`` [N, >= (Hq M Dq + Hkv M Dk + Hkv Dv)], whose query and key heads consist of
     ``maps`` units each: per unit the projection's ``bias`` (float32, over the q, k and v columns) is added, the unit
     RMS-normalised with the weight of its kind ([Dq] / [Dk], shared by all units), and its first ``rotary_dim`` elements
     rotated (element i with i + rotary_dim / 2, angle position * inv_freq[i]).  Query units are written back in place,
     or packed into ``q_out`` [N, Hq M Dq]; key units go to the K pages [page, Hkv, slot, M Dk], value heads (bias added)
-    to the V pages [page, Hkv, slot, Dv].  ``value_dim`` 0: there are no values.  Everything in 32-bit, one rounding."""
+    to the V pages [page, Hkv, slot, Dv].  ``value_dim`` 0: there are no values.  Everything in 32-bit, one rounding.
+
+    ``k_norm_dim`` > 0: only a key unit's first ``k_norm_dim`` elements are normalised (``k_weight`` [k_norm_dim]), the
+    rest stays as projected.  ``q_rot_start`` / ``k_rot_start``: the element of a query / key unit from which the
+    ``rotary_dim`` rotating elements lie (negative: units of that kind do not rotate); ``interleaved``: element 2i pairs
+    with 2i + 1.  ``q_temp`` = (coef, every): query units are multiplied by 1 + coef * ln(floor((p + 1) / every) + 1) at
+    position p."""
     check(qkv, "qkv")
     tokens, row_width = qkv.shape
     weight_dtype = qkv.dtype
-    for name, tensor, size in (("q norm weight", q_weight, q_dim), ("k norm weight", k_weight, k_dim)):
+    for name, tensor, size in (("q norm weight", q_weight, q_dim), ("k norm weight", k_weight, k_norm_dim or k_dim)):
         if tensor is not None:
             check(tensor, name, last_dim=size)
             weight_dtype = tensor.dtype
     if q_weight is not None and k_weight is not None and q_weight.dtype != k_weight.dtype:
         raise KernelError("q and k norm weights must share a dtype")
+    temp_coef, temp_every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 0)
+    if q_temp and temp_every <= 0:
+        raise KernelError(f"the query temperature's period must be positive, got {temp_every}")
     used = (n_q_heads * q_dim + n_kv_heads * k_dim) * maps + n_kv_heads * value_dim
     if bias is not None:
         check(bias, "projection bias", torch.float32)
@@ -348,7 +390,24 @@ def norm_rope_units(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: to
          pointer(inv_freq), positions.data_ptr(), seq_of_token.data_ptr(), block_tables.data_ptr(), block_tables.shape[-1],
          pointer(q_out), k_pages.data_ptr(), pointer(v_pages) if value_dim else 0, tokens, n_q_heads, n_kv_heads, int(maps),
          int(q_dim), int(k_dim), int(value_dim), k_pages.shape[2], k_pages.shape[0], int(write_cache), error_flag.data_ptr(),
-         int(rotary_dim) if inv_freq is not None else 0, dtype_code(qkv.dtype), dtype_code(weight_dtype), stream_handle())
+         int(rotary_dim) if inv_freq is not None else 0, dtype_code(qkv.dtype), dtype_code(weight_dtype), int(k_norm_dim),
+         int(q_rot_start), int(k_rot_start), int(bool(interleaved)), temp_coef, temp_every, stream_handle())
+
+
+def rotate_units(q: torch.Tensor, positions: torch.Tensor, n_heads: int, dim: int, inv_freq: torch.Tensor, rotary_dim: int,
+                 rot_start: int = 0, interleaved: bool = False) -> None:
+    """In place on ``q`` [N, >= n_heads * dim]: ``rotary_dim`` elements of every head, from element ``rot_start`` on, are
+    rotated by the angles position * inv_freq[i] (``norm_rope_units`` for queries alone: nothing is normalised or cached)."""
+    check(q, "q")
+    check(positions, "positions", torch.int32)
+    check(inv_freq, "inv_freq", torch.float32, rotary_dim // 2)
+    tokens, row_width = q.shape
+    if positions.numel() != tokens:
+        raise KernelError("positions need one entry per token")
+    call("llm_norm_rope_units", q.data_ptr(), row_width, 0, 0, 0, 0.0, inv_freq.data_ptr(), positions.data_ptr(), positions.data_ptr(),
+         positions.data_ptr(), 1, 0, 0, 0, tokens, int(n_heads), 0, 1, int(dim), 1, 0, 1, 1, 0, wait_error_flag(q.device).data_ptr(),
+         int(rotary_dim), dtype_code(q.dtype), dtype_code(q.dtype), 0, int(rot_start), -1, int(bool(interleaved)), 0.0, 0,
+         stream_handle())
 
 
 def attention_diff(qkv: torch.Tensor, gate_column: Optional[int], batch, block_tables: torch.Tensor, k_pages: torch.Tensor,
@@ -464,10 +523,12 @@ def tanh_narrow(x: torch.Tensor, act_dtype: torch.dtype) -> torch.Tensor:
     return _pointwise(1, x, None, torch.empty(x.shape, dtype=act_dtype, device=x.device))
 
 
-def softcap_(logits: torch.Tensor, cap: float) -> torch.Tensor:
-    """logits <- cap * tanh(logits / cap), in place on 32-bit values."""
+def softcap_(logits: torch.Tensor, cap: float, scale: float = 1.0) -> torch.Tensor:
+    """logits <- cap * tanh(scale * logits / cap), in place on 32-bit values; without a cap (0), logits <- scale * logits."""
     check(logits, "logits", torch.float32)
-    return _pointwise(2, logits, None, logits, a=cap)
+    if not cap:
+        return _pointwise(3, logits, logits, logits, a=scale, b=0.0)
+    return _pointwise(2, logits, None, logits, a=cap, b=scale)
 
 
 def scaled_sum(x: torch.Tensor, a: float, y: torch.Tensor, b: float) -> torch.Tensor:
@@ -691,13 +752,20 @@ def moe_select(logits: torch.Tensor, correction: Optional[torch.Tensor], top: in
 
 
 def indexed_linear(x: torch.Tensor, weight: torch.Tensor, index: Optional[torch.Tensor], pairs: int, in_div: int = 1,
-                   gated: Optional[tuple] = None, out_dtype: Optional[torch.dtype] = None, cyclic: bool = False) -> torch.Tensor:
+                   gated: Optional[tuple] = None, out_dtype: Optional[torch.dtype] = None, cyclic: bool = False,
+                   in_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[p] = weight[index[p]] x[p // in_div] for p < ``pairs``; ``weight`` is [E, R, K] (``index`` None: E = 1, or,
     ``cyclic``, pair p uses matrix p mod E).
     ``gated`` = (limit, alpha): the matrices hold R gate rows and then R up rows, [E, 2 R, K], and the result is
-    min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + 1)."""
+    min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + up_shift); ``gated`` may carry
+    up_shift as a third number (default 1; (inf, 1, 0) is silu(g) * u).  ``in_scale`` (float32 [pairs]): pair p's input
+    row is multiplied by in_scale[p] as it is read."""
     check(x, "x")
     check(weight, "expert weights", x.dtype, x.shape[-1])
+    if in_scale is not None:
+        check(in_scale, "input scales", torch.float32)
+        if in_scale.numel() < pairs:
+            raise KernelError(f"{in_scale.numel()} input scales for {pairs} pairs")
     if weight.dim() != 3:
         raise KernelError(f"expert weights must be [experts, rows, inner], got {tuple(weight.shape)}")
     rows = weight.shape[1] // 2 if gated else weight.shape[1]
@@ -713,12 +781,19 @@ def indexed_linear(x: torch.Tensor, weight: torch.Tensor, index: Optional[torch.
     if out_dtype not in (x.dtype, torch.float32):
         raise KernelError(f"indexed_linear writes the input's type or float32, not {out_dtype}")
     out = torch.empty((pairs, rows), dtype=out_dtype, device=x.device)
-    limit, alpha = gated if gated else (0.0, 0.0)
+    limit, alpha, up_shift = _gate_constants(gated)
     call("llm_indexed_linear", x.data_ptr(), weight.data_ptr(), pointer(index), out.data_ptr(), pairs, rows, x.shape[-1],
-         int(in_div), int(bool(gated)), float(limit), float(alpha), dtype_code(x.dtype),
+         int(in_div), int(bool(gated)), limit, alpha, dtype_code(x.dtype),
          int(out_dtype == torch.float32 and x.dtype != torch.float32), weight.shape[0] if cyclic and index is None else 0,
-         stream_handle())
+         pointer(in_scale), up_shift, stream_handle())
     return out
+
+
+def _gate_constants(gated: Optional[tuple]):
+    """(limit, alpha, up_shift) of a gated product's activation; up_shift is 1 unless a third number says otherwise."""
+    if not gated:
+        return 0.0, 0.0, 1.0
+    return float(gated[0]), float(gated[1]), float(gated[2]) if len(gated) > 2 else 1.0
 
 
 def moe_combine(down: torch.Tensor, weights: torch.Tensor, shared_out: Optional[torch.Tensor], act_dtype: torch.dtype) -> torch.Tensor:
@@ -778,31 +853,38 @@ def moe_grouped_supported(weight: torch.Tensor, gated: bool) -> bool:
 
 
 def moe_grouped(x: torch.Tensor, weight: torch.Tensor, plan: ExpertPlan, gather_div: Optional[int] = None,
-                gated: Optional[tuple] = None) -> torch.Tensor:
+                gated: Optional[tuple] = None, pair_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One tiled product over all experts: row r of the plan's order gets weight[its expert] times its input row,
     which is x[pair_of_row[r] // gather_div] or, with ``gather_div`` None, x[r].  ``gated`` = (limit, alpha): the
     matrices are [E, 2 R, K], gate rows first, and the result is the experts' activation in bfloat16 [pairs, R];
     otherwise the 32-bit sums [pairs, R].  On tcgen05 where that kernel takes the sizes (it reads its rows by TMA, so
-    rows that have to be gathered are copied into the plan's order first), else the mma.sync kernel."""
+    rows that have to be gathered are copied into the plan's order first), else the mma.sync kernel.  ``pair_scale``
+    (float32 [pairs], with ``gather_div``): the gathered row of pair p is multiplied by pair_scale[p] on the way.
+    ``gated`` may carry the activation's up_shift as a third number (see ``indexed_linear``)."""
     check(x, "x", torch.bfloat16)
+    if pair_scale is not None:
+        check(pair_scale, "pair scales", torch.float32)
+        if gather_div is None or pair_scale.numel() < plan.pairs:
+            raise KernelError("pair scales go with gathered rows, one per pair")
     check(weight, "expert weights", torch.bfloat16, x.shape[-1])
     rows = weight.shape[1] // 2 if gated else weight.shape[1]
     inner = x.shape[-1]
     out = torch.empty((plan.pairs, rows), dtype=torch.bfloat16 if gated else torch.float32, device=x.device)
-    limit, alpha = gated if gated else (0.0, 0.0)
-    if MOE_GROUPED_KERNEL != "mma" and library().llm_moe_grouped_tc_supports(rows, inner, int(bool(gated))) and (gated or rows % 4 == 0):
-        if gather_div is not None:
-            ordered = torch.empty((plan.pairs, inner), dtype=torch.bfloat16, device=x.device)
-            call("llm_moe_gather_rows", x.data_ptr(), plan.pair_of_row.data_ptr(), int(gather_div), ordered.data_ptr(), plan.pairs,
-                 inner, stream_handle())
-            x = ordered
+    limit, alpha, up_shift = _gate_constants(gated)
+    tensor_memory = MOE_GROUPED_KERNEL != "mma" and library().llm_moe_grouped_tc_supports(rows, inner, int(bool(gated))) and (gated or rows % 4 == 0)
+    if gather_div is not None and (tensor_memory or pair_scale is not None):
+        ordered = torch.empty((plan.pairs, inner), dtype=torch.bfloat16, device=x.device)
+        call("llm_moe_gather_rows", x.data_ptr(), plan.pair_of_row.data_ptr(), int(gather_div), ordered.data_ptr(), plan.pairs,
+             inner, pointer(pair_scale), stream_handle())
+        x, gather_div = ordered, None
+    if tensor_memory:
         call("llm_moe_grouped_tc", x.data_ptr(), plan.pairs, weight.data_ptr(), weight.shape[0], plan.tiles.data_ptr(), out.data_ptr(),
-             rows, inner, plan.max_tiles, int(bool(gated)), float(limit), float(alpha), wait_error_flag(x.device).data_ptr(),
+             rows, inner, plan.max_tiles, int(bool(gated)), limit, alpha, up_shift, wait_error_flag(x.device).data_ptr(),
              stream_handle())
         return out
     call("llm_moe_grouped", x.data_ptr(), weight.data_ptr(), plan.tiles.data_ptr(),
          plan.pair_of_row.data_ptr() if gather_div is not None else 0, int(gather_div or 1), out.data_ptr(), rows,
-         inner, plan.max_tiles, int(bool(gated)), float(limit), float(alpha), stream_handle())
+         inner, plan.max_tiles, int(bool(gated)), limit, alpha, up_shift, stream_handle())
     return out
 
 

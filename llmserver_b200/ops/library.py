@@ -26,7 +26,8 @@ SIGNATURES = {
     "llm_attention_generic": [_P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P, _P, _I, _S],
     "llm_rope_kv_write_split": [_P, _P, _F, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _I, _I, _S],
     "llm_normed_add_rmsnorm": [_P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _F, _I, _I, _I, _P, _S],
-    "llm_norm_rope_units": [_P, _I, _P, _P, _P, _F, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _I, _I, _S],
+    "llm_norm_rope_units": [_P, _I, _P, _P, _P, _F, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _S],
+    "llm_scaled_add_rmsnorm": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _F, _I, _I, _I, _S],
     "llm_attention_diff": [_P, _I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _F, _F, _F, _P, _I, _S],
     "llm_attention_diff_mma_supports": [_I, _I, _I, _I],
     "llm_attention_diff_mma": [_P, _I, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _F, _F, _F, _P, _I, _I, _P, _S],
@@ -40,15 +41,15 @@ SIGNATURES = {
     "llm_delta_rule_recurrent": [_P, _I, _I, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P, _P, _S],
     "llm_moe_route": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _S],
     "llm_moe_select": [_P, _P, _P, _P, _I, _I, _I, _F, _S],
-    "llm_indexed_linear": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _S],
+    "llm_indexed_linear": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _I, _I, _I, _P, _F, _S],
     "llm_moe_combine": [_P, _P, _P, _P, _I, _I, _I, _I, _S],
     "llm_clamped_glu": [_P, _P, _I, _I, _F, _F, _I, _S],
     "llm_moe_plan": [_P, _I, _I, _P, _P, _P, _P, _I, _S],
     "llm_moe_grouped_supports": [_I, _I, _I],
-    "llm_moe_grouped": [_P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _F, _S],
+    "llm_moe_grouped": [_P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _F, _F, _F, _S],
     "llm_moe_grouped_tc_supports": [_I, _I, _I],
-    "llm_moe_gather_rows": [_P, _P, _I, _P, _I, _I, _S],
-    "llm_moe_grouped_tc": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _F, _F, _P, _S],
+    "llm_moe_gather_rows": [_P, _P, _I, _P, _I, _I, _P, _S],
+    "llm_moe_grouped_tc": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _F, _F, _F, _P, _S],
     "llm_moe_combine_rows": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _S],
     "llm_gemm_f32": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _S],
     "llm_attention_mma_supports": [_I, _I, _I],

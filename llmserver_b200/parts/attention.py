@@ -28,7 +28,11 @@ class GQAttention(Mixer):
     head where it differs from ``head_dim`` (the output projection then reads heads * value_dim columns).  ``sinks``
     (bool): a learned number per query head joins each softmax's denominator as exp(sink), without a key or a value,
     neither scaled nor masked.  ``precise_weights`` (bool): the design wants its attention weights in 32-bit, so the
-    bfloat16 kernels may not round them to 8 bits for the P V product.  ``names``: pairs (role, tensor name behind the prefix) for checkpoints that call the
+    bfloat16 kernels may not round them to 8 bits for the P V product.  ``values_are_keys`` (bool): there is no value
+    projection, a head's key as projected (and normalised and rotated, where the layer does that) is also its value; the
+    cache then keeps keys alone.  ``unit_sink`` (bool): every softmax denominator holds one more 1 (a sink whose score is
+    0, without a learned number).  ``query_temperature`` = (coef, every): the query at position p is multiplied by
+    1 + coef * ln(floor((p + 1) / every) + 1).  ``names``: pairs (role, tensor name behind the prefix) for checkpoints that call the
     tensors otherwise; roles are q, k, v, o, q_norm, k_norm, sinks.
 
     How positions are encoded comes from the position encoding the layer names (``attach``): its inverse
@@ -39,7 +43,7 @@ class GQAttention(Mixer):
     such heads go through the kernel for heads made of units (pairing "halves" only)."""
 
     KNOWN_PARAMS = ("hidden", "heads", "kv_heads", "head_dim", "scale", "qk_norm", "eps", "window", "bias", "softcap",
-                    "value_dim", "sinks", "names", "precise_weights")
+                    "value_dim", "sinks", "names", "precise_weights", "values_are_keys", "unit_sink", "query_temperature")
     NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
              "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "sinks": "sinks"}
 
@@ -58,6 +62,13 @@ class GQAttention(Mixer):
             raise ValueError("gqa_attention has no biases in its projections (bias must be absent or false)")
         if params.get("softcap"):
             raise ValueError("gqa_attention does not cap attention scores (softcap must be absent or 0)")
+        if params.get("values_are_keys") and params.get("value_dim") and int(params["value_dim"]) != int(params["head_dim"]):
+            raise ValueError("gqa_attention: values that are the keys have the keys' size")
+        if params.get("unit_sink") and params.get("sinks"):
+            raise ValueError("gqa_attention: a softmax has learned sinks or the unit sink, not both")
+        temperature = params.get("query_temperature")
+        if temperature and (len(temperature) != 2 or int(temperature[1]) <= 0):
+            raise ValueError("gqa_attention: query_temperature is (coef, every) with a positive period")
 
     @classmethod
     def declare_weights(cls, params):
@@ -68,6 +79,8 @@ class GQAttention(Mixer):
                   name["k"]: WeightDecl((kv_heads * dim, hidden)),
                   name["v"]: WeightDecl((kv_heads * value_dim, hidden)),
                   name["o"]: WeightDecl((hidden, heads * value_dim))}
+        if params.get("values_are_keys"):
+            del wanted[name["v"]]
         if params.get("qk_norm"):
             wanted[name["q_norm"]] = WeightDecl((dim,), NORM)
             wanted[name["k_norm"]] = WeightDecl((dim,), NORM)
@@ -77,6 +90,8 @@ class GQAttention(Mixer):
 
     @classmethod
     def cache_need(cls, params):
+        if params.get("values_are_keys"):
+            return KVPagesNeed(int(params["kv_heads"]), int(params["head_dim"]), params.get("window"), None, keys_only=True)
         return KVPagesNeed(int(params["kv_heads"]), int(params["head_dim"]), params.get("window"),
                            int(params["value_dim"]) if params.get("value_dim") else None)
 
@@ -92,11 +107,18 @@ class GQAttention(Mixer):
         # keys and values of different sizes are rotated and cached by the kernel for split sizes
         self.split = self.value_dim != self.head_dim
         name = self.names(params)
-        self.qkv = torch.cat([weights[name["q"]], weights[name["k"]], weights[name["v"]]], dim=0).contiguous()
+        self.values_are_keys = bool(params.get("values_are_keys"))
+        self.temperature = tuple(params["query_temperature"]) if params.get("query_temperature") else None
+        self.qkv = torch.cat([weights[name["q"]], weights[name["k"]]] + ([] if self.values_are_keys else [weights[name["v"]]]),
+                             dim=0).contiguous()
         self.out = weights[name["o"]].contiguous()
         self.q_norm = weights[name["q_norm"]].contiguous() if params.get("qk_norm") else None
         self.k_norm = weights[name["k_norm"]].contiguous() if params.get("qk_norm") else None
         self.sinks = weights[name["sinks"]].to(torch.float32).contiguous() if params.get("sinks") else None
+        if params.get("unit_sink"):
+            self.sinks = torch.zeros(self.heads, dtype=torch.float32, device=runtime.device)      # exp(0): a one in every denominator
+        # keys that are their own values and queries with a temperature go through the kernel for heads made of units
+        self.by_units = self.values_are_keys or self.temperature is not None
         self.inv_freq, self.rotary_dim, self.interleaved, self.magnitude = None, self.head_dim, False, 1.0
 
     def attach(self, position):
@@ -117,22 +139,40 @@ class GQAttention(Mixer):
             raise ValueError(f"gqa_attention pairs rotated elements as 'halves' or 'interleaved', not {pairing!r}")
         self.magnitude = float(getattr(position, "attention_factor", 1.0))
         if self.magnitude != 1.0:
+            if self.by_units:
+                raise ValueError("gqa_attention: the kernel for heads made of units does not scale the rotated values, and the "
+                                 f"position encoding's attention_factor is {self.magnitude}")
             if self.q_norm is not None:
                 raise ValueError("gqa_attention: the rotation kernel that applies per-head Q/K norms does not scale the rotated "
                                  f"values, and the position encoding's attention_factor is {self.magnitude}")
             self.split = True
         self.inv_freq, self.rotary_dim, self.interleaved = inv_freq, rotary_dim, pairing == "interleaved"
-        if self.interleaved and self.split and self.q_norm is not None:
+        if self.interleaved and self.split and self.q_norm is not None and not self.by_units:
             raise ValueError("gqa_attention: per-head Q/K norms with values of another size than the keys rotate in halves only")
 
     feeds_stream = True
 
     @functools.cached_property
     def takes_unscaled(self):
-        return not self.split and ops.unscaled_rows_supported(self.qkv)
+        return not self.split and not self.by_units and ops.unscaled_rows_supported(self.qkv)
 
     def forward(self, x, batch, cache, sink=None):
         tables = batch.block_tables[cache.group]
+        if self.by_units:
+            # one unit per head: norms, temperature, rotation and the cache write in one kernel; without a value projection
+            # the packed row ends behind the keys and the V pages are the K pages
+            qkv = ops.linear(x, self.qkv)
+            rotating = self.rotary_dim if self.inv_freq is not None else 0
+            ops.norm_rope_units(qkv, batch.positions, batch.seq_of_token, tables, cache.k_pages,
+                                None if self.values_are_keys else cache.v_pages, self.heads, self.kv_heads, 1, self.head_dim,
+                                self.head_dim, 0 if self.values_are_keys else self.value_dim, batch.error_flag,
+                                q_weight=self.q_norm, k_weight=self.k_norm, eps=self.eps, inv_freq=self.inv_freq,
+                                rotary_dim=rotating, write_cache=cache.writes, interleaved=self.interleaved,
+                                q_temp=self.temperature)
+            attended = ops.attention(qkv, batch, tables, cache.k_pages, cache.v_pages, self.heads, self.kv_heads, self.head_dim,
+                                     self.scale, self.window, value_dim=self.value_dim, sinks=self.sinks,
+                                     precise=bool(self.params.get("precise_weights")), q_stride=qkv.shape[1])
+            return ops.linear(attended, self.out, sink=sink)
         if self.split and self.q_norm is not None:
             # heads with a norm whose values have another size than their keys: the kernel for heads made of units, one
             # unit per head

@@ -2,7 +2,10 @@
 from __future__ import annotations
 
 from .base import Block
-from .norm import NormedDelta, add_and_read
+import torch
+
+from ..weights.declare import NORM, WeightDecl
+from .norm import NormedDelta, ScaledDelta, add_and_read
 from .registry import BLOCKS
 
 
@@ -100,3 +103,55 @@ class OutputNormBlock(Block):
             return residual, pending
         out = self.feed_forward.forward(add_and_read(residual, pending, act))
         return residual, NormedDelta(out, self.feed_forward_out_norm, bias=getattr(self.feed_forward, "output_bias", None))
+
+
+@BLOCKS.register("parallel_residual")
+class ParallelResidualBlock(Block):
+    """One norm whose output both sub-layers read, and one sum:
+
+        n = mixer_norm(h);  h += s1 * mixer(n) + s2 * feed_forward(n)
+
+    with a learned scale per channel on each sub-layer's output (``layer_scale``; without it s1 = s2 = 1).  Nothing is
+    added here: both outputs travel on as a ``ScaledDelta`` and the next norm's kernel (the next block's, or the model's
+    final norm) multiplies, adds them to the 32-bit stream and normalises it.  Parameters: ``width``; ``feed_forward``
+    (default True; False: the layer is its mixer alone); ``layer_scale`` (default False); the tensor-name prefixes of its
+    parts (``mixer_prefix``, ``feed_forward_prefix``, ``mixer_norm_prefix``) and, behind the layer's prefix, the names of
+    the two scales (``mixer_scale``, ``feed_forward_scale``)."""
+
+    KNOWN_PARAMS = ("width", "feed_forward", "layer_scale", "mixer_prefix", "feed_forward_prefix", "mixer_norm_prefix",
+                    "mixer_scale", "feed_forward_scale")
+
+    @classmethod
+    def roles(cls, params):
+        roles = {"mixer": "mixer", "mixer_norm": "norm"}
+        if params.get("feed_forward", True):
+            roles["feed_forward"] = "feed_forward"
+        return roles
+
+    @classmethod
+    def declare_weights(cls, params):
+        if not params.get("layer_scale"):
+            return {}
+        wanted = {params.get("mixer_scale", "mixer_scale"): WeightDecl((int(params["width"]),), NORM)}
+        if params.get("feed_forward", True):
+            wanted[params.get("feed_forward_scale", "feed_forward_scale")] = WeightDecl((int(params["width"]),), NORM)
+        return wanted
+
+    def __init__(self, params, parts, weights=None):
+        super().__init__(params, parts)
+        device = self.mixer.runtime.device
+
+        def scale(name):
+            if params.get("layer_scale"):
+                return weights[params.get(name, name)].to(torch.float32).contiguous()
+            return torch.ones(int(params["width"]), dtype=torch.float32, device=device)
+
+        self.mixer_scale = scale("mixer_scale")
+        self.feed_forward_scale = scale("feed_forward_scale") if params.get("feed_forward", True) else None
+
+    def forward(self, residual, delta, batch, cache):
+        normed = self.mixer_norm.add_norm(residual, delta)
+        pending = [(self.mixer.forward(normed, batch, cache), self.mixer_scale)]
+        if self.params.get("feed_forward", True):
+            pending.append((self.feed_forward.forward(normed), self.feed_forward_scale))
+        return residual, ScaledDelta(pending)

@@ -24,6 +24,14 @@ class NormedDelta:
     bias: Optional[torch.Tensor] = None
 
 
+@dataclass
+class ScaledDelta:
+    """The outputs of sub-layers that read the same normalised stream and join it together, each through a learned scale
+    per channel (float32 [width]): ``parts`` is a list of (output, scale).  The next norm's kernel multiplies, adds all of
+    them to the 32-bit stream and normalises it in one pass."""
+    parts: list
+
+
 def add_and_read(residual: torch.Tensor, delta, act_dtype: torch.dtype) -> torch.Tensor:
     """Adds what is pending (a ``NormedDelta`` or nothing) to the 32-bit stream and returns the stream itself in the
     activation type: the input of a sub-layer that reads the stream without a norm in front."""
@@ -64,6 +72,13 @@ class RMSNorm(Norm):
             return ops.normed_add_rmsnorm(residual, delta.delta, post.weight if post is not None else None,
                                           post.eps if post is not None else 0.0, self.weight, self.eps,
                                           extra=delta.extra, rows=rows, act_dtype=self.runtime.dtype, delta_bias=delta.bias)
+        if isinstance(delta, ScaledDelta):
+            (first, first_scale), second = delta.parts[0], (delta.parts[1] if len(delta.parts) > 1 else (None, None))
+            for extra, extra_scale in delta.parts[2:]:      # more than two sub-layers: the others join the stream first
+                ops.scaled_add_rmsnorm(residual, extra, extra_scale, None, None, None, 0.0, act_dtype=self.runtime.dtype,
+                                       want_output=False)
+            return ops.scaled_add_rmsnorm(residual, first, first_scale, second[0], second[1], self.weight, self.eps, rows=rows,
+                                          act_dtype=self.runtime.dtype)
         if isinstance(delta, ops.StreamSink):
             # the part in front added its result to the stream itself and, if asked, prepared this norm's input
             if delta.owner is not self or not delta.added:

@@ -23,6 +23,9 @@ def declared_weights(spec) -> Dict[str, WeightDecl]:
 
     wanted: Dict[str, WeightDecl] = {spec.embedding_name: WeightDecl((spec.vocab_size, spec.hidden_size))}
     for layer in spec.layers:
+        # what the block arrangement itself reads (scales on its sub-layers' outputs, say) lies behind the layer's prefix
+        for local, declaration in parts.BLOCKS.get(layer.block.kind).declare_weights(layer.block.as_dict()).items():
+            wanted[layer.prefix + local] = declaration
         for _, part_spec, part_cls, prefix in parts.parts_of_layer(layer):
             for local, declaration in part_cls.declare_weights(part_spec.as_dict()).items():
                 wanted[prefix + local] = declaration
