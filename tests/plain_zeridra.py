@@ -64,8 +64,9 @@ def query_temperature(positions, q_temp):
     return 1.0 + float(q_temp["coef"]) * torch.log(steps + 1.0)
 
 
-def attention_mixer(h, positions, mixer, weights, prefix):
-    """Grouped-query attention without rotation and without a value projection: a key is also its value."""
+def attention_mixer(h, positions, mixer, weights, prefix, one_more=True):
+    """Grouped-query attention without rotation and without a value projection: a key is also its value.  ``one_more``
+    False leaves the one out of the denominator (a deliberately wrong model)."""
     heads, groups, dim = int(mixer["heads"]), int(mixer["kv_heads"]), int(mixer["dim"])
     T = h.shape[0]
     q = (h @ weights[prefix + "q"].to(F).T).view(T, heads, dim)
@@ -73,7 +74,7 @@ def attention_mixer(h, positions, mixer, weights, prefix):
     q = q * query_temperature(positions, mixer.get("q_temp")).view(T, 1, 1)
     k = k.repeat_interleave(heads // groups, dim=1)
     scores = torch.einsum("ihd,jhd->hij", q, k) * float(mixer["scale"])
-    p = softmax_with_extra(scores, visible(positions), torch.zeros(heads))
+    p = softmax_with_extra(scores, visible(positions), torch.zeros(heads) if one_more else torch.full((heads,), -1e30))
     out = torch.einsum("hij,jhd->ihd", p, k).reshape(T, heads * dim)
     return out @ weights[prefix + "o"].to(F).T
 
@@ -88,7 +89,7 @@ def latent_kv(h, positions, mixer, weights, prefix, eps):
 
 def latent_mixer(h, positions, mixer, weights, prefix, eps, kv, window_shift=0):
     """``kv`` = (c [T, kv_rank], turned key part [T, rot_dim]): the layer's own, or those of the layer it names."""
-    heads, dim, rot_dim, vdim = int(mixer["heads"]), int(mixer["dim"]), int(mixer["rot_dim"]), int(mixer["vdim"])
+    heads, dim, rot_dim, vdim = int(mixer["heads"]), int(mixer["dim"]), int(mixer.get("rot_dim") or 0), int(mixer["vdim"])
     T = h.shape[0]
     c, k_turn = kv
     c_q = rms_norm(h @ weights[prefix + "dq"].to(F).T, weights[prefix + "dq.norm"], eps)
@@ -116,19 +117,29 @@ def expert(x, weights, prefix):
     return (gate * torch.sigmoid(gate) * up) @ weights[prefix + "down"].to(F).T
 
 
+def route_margin(h, mlp, weights, prefix):
+    """Per token, the gap between the last chosen score and the best one left out (inf when every expert is chosen)."""
+    s = torch.sort(torch.sigmoid(h @ weights[prefix + "router"].to(F).T), dim=-1, descending=True).values
+    top = int(mlp["router"]["top"])
+    return s[:, top - 1] - s[:, top] if top < s.shape[1] else torch.full((h.shape[0],), math.inf, dtype=F)
+
+
 def feed_forward(h, mlp, weights, prefix):
     """sum over a token's chosen experts e of expert_e(score_e * h): the score multiplies what goes in."""
     chosen, scores = route(h, mlp, weights, prefix)
     out = torch.zeros_like(h)
-    for t in range(h.shape[0]):
-        for e, s in zip(chosen[t].tolist(), scores[t]):
-            out[t] += expert(s * h[t], weights, f"{prefix}e{e}.")
+    for e in range(int(mlp["router"]["experts"])):
+        for slot in range(chosen.shape[1]):
+            rows = (chosen[:, slot] == e).nonzero().flatten()
+            if rows.numel():
+                out[rows] += expert(scores[rows, slot, None] * h[rows], weights, f"{prefix}e{e}.")
     return out
 
 
-def forward(config, weights, tokens, keep_layers=False, window_shift=0, drop_sinks=False):
+def forward(config, weights, tokens, keep_layers=False, window_shift=0, drop_sinks=False, margins=None):
     """Logits [T, vocab] of one sequence (and, with ``keep_layers``, the stream behind every layer).  ``window_shift``
-    and ``drop_sinks`` make deliberately wrong models for the tests that show a fault would be seen."""
+    and ``drop_sinks`` make deliberately wrong models for the tests that show a fault would be seen.  ``margins`` (a
+    list): gets one tensor [T], the smallest routing margin of each token over all layers."""
     eps = float(config["norm"]["eps"])
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     positions = torch.arange(tokens.shape[0])
@@ -138,9 +149,7 @@ def forward(config, weights, tokens, keep_layers=False, window_shift=0, drop_sin
         prefix, mixer = f"l{index}.", layer["mixer"]
         h = rms_norm(x, weights[prefix + "norm1"], eps)
         if layer["type"] == "attention":
-            mixed = attention_mixer(h, positions, mixer, weights, prefix + "mix.")
-            if drop_sinks:
-                raise NotImplementedError
+            mixed = attention_mixer(h, positions, mixer, weights, prefix + "mix.", one_more=not drop_sinks)
         else:
             if mixer.get("kv_from") is None:
                 left[index] = latent_kv(h, positions, mixer, weights, prefix + "mix.", eps)
@@ -151,6 +160,9 @@ def forward(config, weights, tokens, keep_layers=False, window_shift=0, drop_sin
                                  left[index if mixer.get("kv_from") is None else int(mixer["kv_from"])], window_shift)
         x = x + mixed * weights[prefix + "ls1"].to(F)
         if layer.get("mlp") is not None:
+            if margins is not None:
+                margin = route_margin(h, layer["mlp"], weights, prefix + "mlp.")
+                margins[:] = [margin if not margins else torch.minimum(margins[0], margin)]
             x = x + feed_forward(h, layer["mlp"], weights, prefix + "mlp.") * weights[prefix + "ls2"].to(F)
         streams.append(x.clone())
     logits = rms_norm(x, weights["final.norm"], eps) @ weights["head"].to(F).T * float(config.get("logit_scale", 1.0))
