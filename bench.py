@@ -259,6 +259,58 @@ def vibepel_comparison(args) -> int:
     return 0
 
 
+def zeridra_comparison(args) -> int:
+    """Zeridra beside the Gefarax model of equal size (grouped attention with keys and values of 128 and the same routed
+    experts): a 2048-token prompt in one step and decode steps at batch 1, 8 and 64 (contexts averaging 3072),
+    device-timed like the headline run; bytes and FLOPs counted per step, fractions of the measured peaks.  Random
+    bfloat16 weights; four layers of one kind of mixer, or a mix with a layer that reads another layer's cache."""
+    from llmserver_b200.cli.harness import (ZERIDRA_SIZES, zeridra_config, zeridra_gefarax_twin, zeridra_step_cost, zeridra_twin_cost)
+    import llmserver_b200.models  # noqa: F401
+
+    os.environ["PATH"] = os.path.dirname(sys.executable) + os.pathsep + os.environ.get("PATH", "")
+    layers = args.layers if "--layers" in " ".join(sys.argv) else 4
+    peaks, peak_source = read_peaks()
+    wanted = args.sizes.split(",") if args.sizes else list(ZERIDRA_SIZES)
+    steps, warmup = min(args.steps, 32), max(3, min(args.warmup, 4))
+    results, twin_done = {}, {}
+    with ClockSampler() as clocks:
+        for name in wanted:
+            size = ZERIDRA_SIZES[name]
+            results[name] = {"kinds": list(size["kinds"])}
+            arms = [("zeridra", size, zeridra_config(size, layers), zeridra_step_cost)]
+            if size["width"] not in twin_done:
+                twin, twin_config = zeridra_gefarax_twin(size, layers)
+                arms.append(("gefarax", twin, twin_config, zeridra_twin_cost))
+            for label, sizes, config, cost in arms:
+                harness = Harness(layers, 64, config=config)
+                row = {}
+                prefill_ms = harness.time_prefill(PROMPT)
+                _, flops = cost(sizes, layers, PROMPT, 1, 0)
+                row["prefill"] = {"ms": round(prefill_ms, 3), "tokens_per_s": round(PROMPT / prefill_ms * 1e3),
+                                  "tflops": round(flops / prefill_ms / 1e9, 1),
+                                  "frac_of_bf16_burst": round(flops / prefill_ms / 1e9 / peaks["bf16_tflops"], 3)}
+                for batch in (1, 8, 64):
+                    harness.time_decode(batch, 4, 3)
+                    run = harness.time_decode(batch, steps, warmup)
+                    bytes_, _ = cost(sizes, layers, batch, batch, run["mean_context"])
+                    gbs = bytes_ / run["ms_per_step"] / 1e6
+                    row[f"decode_b{batch}"] = {"ms": round(run["ms_per_step"], 4), "tokens_per_s": round(run["tokens_per_s"], 1),
+                                               "gb_per_step": round(bytes_ / 1e9, 3), "gbs": round(gbs, 1),
+                                               "frac_of_copy": round(gbs / peaks["hbm_gbs"], 3),
+                                               "graph_steps": harness.step_function.graph_steps}
+                if label == "gefarax":
+                    twin_done[size["width"]] = row
+                else:
+                    results[name][label] = row
+                harness.close()
+            results[name]["gefarax"] = twin_done[size["width"]]
+    print(json.dumps({"design": "zeridra", "beside": "Gefarax of equal width, heads (keys and values of 128) and routed experts",
+                      "layers": layers, "prompt": PROMPT, "decode_context_mean": MEAN_DECODE_CONTEXT, "dtype": "bf16",
+                      "data": "synthetic: seeded random weights, uniform random token ids", "peaks": {**peaks, "source": peak_source},
+                      "clocks": clocks.summary(), "sizes": results}))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--gpus", type=int, default=1)
@@ -269,7 +321,7 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--skip-points", action="store_true", help="skip the batch-1 and batch-64 points")
-    parser.add_argument("--design", default=None, choices=["gefarax", "dikusun", "vibepel"],
+    parser.add_argument("--design", default=None, choices=["gefarax", "dikusun", "vibepel", "zeridra"],
                         help="instead of the headline run: prefill and decode of this design at a few layer sizes, beside the "
                              "dense decoder of equal size (one JSON line; --layers defaults to 4 here)")
     parser.add_argument("--sizes", default=None, help="with --design: comma-separated names of the sizes to run (default: all)")
@@ -278,6 +330,8 @@ def main() -> int:
         return design_comparison(args)
     if args.design == "dikusun":
         return dikusun_comparison(args)
+    if args.design == "zeridra":
+        return zeridra_comparison(args)
     if args.design == "vibepel":
         return vibepel_comparison(args)
     if args.warmup < 3:

@@ -517,3 +517,104 @@ def vibepel_step_cost(size: dict, layers: int, tokens: int, sequences: int, cont
         total_bytes += 2.0 * weights
         flops += 2.0 * tokens * weights
     return total_bytes, flops
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Zeridra beside Gefarax (the closest design: grouped attention with a term of its own in the denominator, routed gated
+# experts under a sigmoid router) at equal size
+# ---------------------------------------------------------------------------------------------------------------------
+def _zeridra_mixers(width, heads, kv_heads):
+    """Mixers of one width: attention with heads of 128 whose keys are its values, warmed-up queries; latent attention
+    with 16 heads of 64 still and 32 turning elements through a query latent of a quarter of the width and a cached row
+    of 96 + 32 (the widest the tensor-core attention kernels take), values of 128, a window of 1024."""
+    return (dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, scale=128 ** -0.5, q_temp={"coef": 0.1, "every": 1024}),
+            dict(heads=16, dim=64, rot_dim=32, vdim=128, q_rank=width // 4, kv_rank=96, scale=96 ** -0.5, mask={"size": 1024},
+                 rot={"base": 500000.0, "dims": 32}))
+
+
+# Layer sizes that resemble served models: four layers of one kind of mixer, or attention, latent, attention and a latent
+# layer that reads the second layer's cache; every layer has routed experts (the sizes of Gefarax's comparison).
+ZERIDRA_SIZES = {}
+for _width, _heads, _kv, _experts, _top, _ff in ((2048, 16, 4, 32, 4, 768), (4096, 32, 8, 64, 6, 1792)):
+    _a, _l = _zeridra_mixers(_width, _heads, _kv)
+    for _label, _kinds in (("attention", ("attention",) * 4), ("latent", ("latent_attention",) * 4),
+                           ("mixed", ("attention", "latent_attention", "attention", "shared_latent"))):
+        ZERIDRA_SIZES[f"w{_width}-{_label}"] = dict(width=_width, attention=_a, latent=_l, experts=_experts, top=_top, ff=_ff, kinds=_kinds)
+
+
+def _zeridra_kinds(size: dict, layers: int):
+    return [size["kinds"][index % len(size["kinds"])] for index in range(layers)]
+
+
+def zeridra_config(size: dict, layers: int = None):
+    from llmserver_b200.config import ZeridraConfig
+    kinds = _zeridra_kinds(size, layers or len(size["kinds"]))
+    made, owner = [], None
+    for index, kind in enumerate(kinds):
+        if kind == "attention":
+            mixer = dict(size["attention"])
+        else:
+            mixer = dict(size["latent"])
+            if kind == "shared_latent" and owner is not None:
+                mixer["kv_from"] = owner
+            else:
+                owner = index
+        made.append({"type": "attention" if kind == "attention" else "latent_attention", "mixer": mixer,
+                     "mlp": {"kind": "moe", "router": {"experts": size["experts"], "top": size["top"]}, "expert": {"ff": size["ff"]}}})
+    return ZeridraConfig.from_dict({"architecture": "Zeridra", "vocab": COMPARE_VOCAB, "width": size["width"], "norm": {"eps": 1e-6},
+                                    "embedding": {"scale": size["width"] ** 0.5}, "logit_scale": 0.25, "logit_softcap": 30.0,
+                                    "layers": made})
+
+
+def zeridra_gefarax_twin(size: dict, layers: int):
+    """The Gefarax model of equal size: the same width, the attention layers' heads (keys and values of 128, all of a key
+    rotating), the same experts, no shared expert."""
+    a = size["attention"]
+    twin = _gefarax_size(size["width"], a["heads"], a["kv_heads"], a["dim"], a["vdim"], size["experts"], size["top"], size["ff"], 0)
+    raw = gefarax_config(dict(twin, shared_ff=8), layers).to_dict()
+    for layer in raw["layers"]:
+        layer["mlp"]["shared"] = None
+    from llmserver_b200.config import GefaraxConfig
+    return twin, GefaraxConfig.from_dict(raw)
+
+
+def zeridra_twin_cost(size: dict, layers: int, tokens: int, sequences: int, context: float):
+    per_sequence = tokens / sequences
+    pairs = sequences * (per_sequence * context + per_sequence * (per_sequence + 1) / 2)
+    return gefarax_step_cost(size, layers, tokens, sequences * (context + per_sequence), pairs)
+
+
+def zeridra_step_cost(size: dict, layers: int, tokens: int, sequences: int, context: float):
+    """(bytes, FLOPs) of one step in which each of ``sequences`` requests brings tokens / sequences new tokens behind
+    ``context`` cached ones: bytes = every weight the step touches once (of the routed experts the expected number of
+    distinct ones its tokens choose) + the cached rows its mixers read (a key that is its own value counts once);
+    FLOPs = the products of the tokens + attention per (query, key) pair as the design defines it (latent layers: keys of
+    dim + rot_dim and values of vdim per head)."""
+    width, experts, top, ff = size["width"], size["experts"], size["top"], size["ff"]
+    per_sequence = tokens / sequences
+    total_bytes = COMPARE_VOCAB * width * 2.0
+    flops = 0.0
+    distinct = experts * (1.0 - (1.0 - top / experts) ** tokens)
+    for kind in _zeridra_kinds(size, layers):
+        total_bytes += 2.0 * 3 * width * distinct * ff + 4.0 * experts * width
+        flops += 2.0 * tokens * (3 * width * top * ff + experts * width)
+        if kind == "attention":
+            m = size["attention"]
+            heads, kv, dim = m["heads"], m["kv_heads"], m["dim"]
+            weights = (heads + kv) * dim * width + width * heads * dim
+            total_bytes += sequences * (context + per_sequence) * kv * dim * 2.0
+            pairs = sequences * (per_sequence * context + per_sequence * (per_sequence + 1) / 2)
+            flops += 2.0 * heads * 2 * dim * pairs
+        else:
+            m = size["latent"]
+            heads, dim, rot, vdim, q_rank, kv_rank, window = (m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["q_rank"], m["kv_rank"],
+                                                             m["mask"]["size"])
+            weights = q_rank * width + heads * (dim + rot) * q_rank + heads * dim * kv_rank + heads * vdim * kv_rank + width * heads * vdim
+            if kind != "shared_latent":
+                weights += (kv_rank + rot) * width
+            total_bytes += sequences * min(context + per_sequence, window) * (kv_rank + rot) * 2.0
+            pairs = sequences * sum(min(context + i + 1, window) for i in range(int(per_sequence)))
+            flops += 2.0 * heads * (dim + rot + vdim) * pairs
+        total_bytes += 2.0 * weights
+        flops += 2.0 * tokens * weights
+    return total_bytes, flops
