@@ -203,7 +203,9 @@ __device__ __forceinline__ void load_kv_tile(__nv_bfloat16* k_tile, __nv_bfloat1
         }
         const int destination = swizzled<D>(row, chunk);
         cp_async_16(smem_address(k_tile + destination), p.k_pages + offset, valid ? 16 : 0);
-        if (DV == D) cp_async_16(smem_address(v_tile + destination), p.v_pages + offset, valid ? 16 : 0);
+        // a cache of keys that are also the values (the same pages handed in twice) is staged once: the caller reads
+        // its values from the key tile
+        if (DV == D && p.v_pages != p.k_pages) cp_async_16(smem_address(v_tile + destination), p.v_pages + offset, valid ? 16 : 0);
     }
     if (DV != D) {      // values of another size than keys: rows of DV elements, walked the same way
         constexpr int kValueChunks = DV / 8;
@@ -417,7 +419,7 @@ __global__ void __launch_bounds__(kThreads) attention_portions_kernel(const Attn
     for (int it = 0; it < n_tiles; ++it) {
         const int stage = it & 1;
         __nv_bfloat16* k_tile = kv_tiles + stage * kStage;
-        __nv_bfloat16* v_tile = k_tile + kTileKeys * D;
+        __nv_bfloat16* v_tile = (DV == D && p.v_pages == p.k_pages) ? k_tile : k_tile + kTileKeys * D;
         if (it + 1 < n_tiles) {
             __nv_bfloat16* next_k = kv_tiles + (stage ^ 1) * kStage;
             load_kv_tile<D, DV>(next_k, next_k + kTileKeys * D, p, table, kv_head, first_tile_key + (it + 1) * kTileKeys, context);
@@ -538,7 +540,7 @@ __global__ void __launch_bounds__(kThreads) attention_decode_kernel(const AttnPa
     for (int it = 0; it < n_tiles; ++it) {
         const int stage = it & 1;
         __nv_bfloat16* k_tile = kv_tiles + stage * kStage;
-        __nv_bfloat16* v_tile = k_tile + kTileKeys * D;
+        __nv_bfloat16* v_tile = (DV == D && p.v_pages == p.k_pages) ? k_tile : k_tile + kTileKeys * D;
         if (it + 1 < n_tiles) {
             __nv_bfloat16* next_k = kv_tiles + (stage ^ 1) * kStage;
             load_kv_tile<D, DV>(next_k, next_k + kTileKeys * D, p, table, kv_head, split_begin + (it + 1) * kTileKeys, split_end);

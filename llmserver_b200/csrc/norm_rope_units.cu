@@ -84,14 +84,19 @@ __global__ void norm_rope_units_kernel(T* __restrict__ qkv, int row_width, const
             }
         }
         const int norm_dim = (is_k && k_norm_dim > 0) ? k_norm_dim : dim;
+        const W* weight = is_q ? q_weight : (is_k ? k_weight : nullptr);
+        const int rot_start = is_q ? q_rot_start : (is_k ? k_rot_start : -1);
+        const int turning = (inv_freq && rot_start >= 0) ? rotary_dim : 0;
+        // a query unit that stays where it lies and only turns: nothing but its turning elements is read or written
+        const bool only_turns = is_q && !q_out && !weight && !bias && temp_every <= 0;
+        const int from = only_turns ? rot_start : 0, upto = only_turns ? rot_start + turning : dim;
         float sum_squares = 0.0f;
-        for (int i = lane; i < dim; i += 32) {
+        for (int i = from + lane; i < upto; i += 32) {
             float v = Num<T>::load(row + column + i);
             if (bias) v += bias[column + i];
             values[i] = v;
             if (i < norm_dim) sum_squares += v * v;
         }
-        const W* weight = is_q ? q_weight : (is_k ? k_weight : nullptr);
         if (weight) {
             const float inverse = rsqrtf(warp_sum(sum_squares) / (float)norm_dim + eps);
             for (int i = lane; i < norm_dim; i += 32) values[i] = values[i] * inverse * Num<W>::load(weight + i);
@@ -101,8 +106,6 @@ __global__ void norm_rope_units_kernel(T* __restrict__ qkv, int row_width, const
             for (int i = lane; i < dim; i += 32) values[i] *= factor;
         }
         __syncwarp();
-        const int rot_start = is_q ? q_rot_start : (is_k ? k_rot_start : -1);
-        const int turning = (inv_freq && rot_start >= 0) ? rotary_dim : 0;
         for (int i = lane; i < turning / 2; i += 32) {
             const float c = rotation[i].x, s = rotation[i].y;
             const int first = rot_start + (interleaved ? 2 * i : i), second = interleaved ? first + 1 : first + half;
@@ -110,8 +113,9 @@ __global__ void norm_rope_units_kernel(T* __restrict__ qkv, int row_width, const
             Num<T>::store(dst + first, u * c - v * s);
             Num<T>::store(dst + second, v * c + u * s);
         }
-        for (int i = lane; i < dim; i += 32)
-            if (turning == 0 || i < rot_start || i >= rot_start + turning) Num<T>::store(dst + i, values[i]);
+        if (!only_turns)
+            for (int i = lane; i < dim; i += 32)
+                if (turning == 0 || i < rot_start || i >= rot_start + turning) Num<T>::store(dst + i, values[i]);
         __syncwarp();      // the next unit of this warp overwrites the values
     }
 }

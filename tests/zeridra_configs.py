@@ -23,13 +23,14 @@ def _moe(experts, top, ff):
     return {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff}}
 
 
+# sizes that are a multiple of nothing much: a width of 44, heads of 10 and 14 elements, experts of 18 and 27 rows
 ATTENTION_ONLY = {
-    "architecture": "Zeridra", "vocab": 211, "width": 48, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+    "architecture": "Zeridra", "vocab": 211, "width": 44, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
     "logit_scale": 1.0,
     "layers": [
-        {"type": "attention", "mixer": _attention(3, 3, 16, 0.25, (0.5, 7)), "mlp": None},
-        {"type": "attention", "mixer": _attention(6, 2, 8, 0.35), "mlp": _moe(5, 2, 24)},
-        {"type": "attention", "mixer": _attention(2, 1, 24, 0.2, (0.2, 1)), "mlp": _moe(3, 3, 40)},
+        {"type": "attention", "mixer": _attention(3, 3, 14, 0.25, (0.5, 7)), "mlp": None},
+        {"type": "attention", "mixer": _attention(6, 2, 10, 0.35), "mlp": _moe(5, 2, 18)},
+        {"type": "attention", "mixer": _attention(2, 1, 24, 0.2, (0.2, 1)), "mlp": _moe(3, 3, 27)},
     ],
 }
 
