@@ -562,7 +562,7 @@ def zeridra_config(size: dict, layers: int = None):
         made.append({"type": "attention" if kind == "attention" else "latent_attention", "mixer": mixer,
                      "mlp": {"kind": "moe", "router": {"experts": size["experts"], "top": size["top"]}, "expert": {"ff": size["ff"]}}})
     return ZeridraConfig.from_dict({"architecture": "Zeridra", "vocab": COMPARE_VOCAB, "width": size["width"], "norm": {"eps": 1e-6},
-                                    "embedding": {"scale": size["width"] ** 0.5}, "logit_scale": 0.25, "logit_softcap": 30.0,
+                                    "embedding": {"scale": size["width"] ** 0.5}, "logit_scale": 0.5, "logit_softcap": 50.0,
                                     "layers": made})
 
 

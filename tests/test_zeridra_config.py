@@ -78,7 +78,7 @@ def test_specification_parts_and_constants():
     assert [entry.cache_from for entry in spec.schedule] == [None, None, 0, None, None, 4, 4]
     assert spec.embedding_scale == 0.7 and spec.logit_scale == 2.0 and spec.logit_softcap == 25.0
     attention = spec.layers[1].mixer.as_dict()
-    assert attention["values_are_keys"] and attention["unit_sink"] and attention["query_temperature"] == (0.3, 16)
+    assert attention["values_are_keys"] and attention["unit_sink"] and attention["query_temperature"] == (0.4, 16)
     assert spec.layers[3].mixer.as_dict()["query_temperature"] is None
     experts = spec.layers[0].feed_forward.as_dict()
     assert (experts["activation"], experts["weight_on"], experts["correction"], experts["top"]) == ("silu", "input", False, 2)

@@ -51,9 +51,9 @@ ALL_KINDS = {
     "architecture": "Zeridra", "vocab": 300, "width": 96, "norm": {"eps": 1e-6}, "embedding": {"scale": 0.7},
     "logit_scale": 2.0, "logit_softcap": 25.0,
     "layers": [
-        {"type": "latent_attention", "mixer": _latent(4, 16, 16, 24, 40, 56, 0.18, 23, 16, base=1e6), "mlp": _moe(6, 2, 32)},
-        {"type": "attention", "mixer": _attention(4, 2, 24, 0.2, (0.3, 16)), "mlp": _moe(9, 1, 48)},
-        {"type": "latent_attention", "mixer": _latent(2, 32, 16, 48, 24, 56, 0.15, 61, 16, base=1e6, kv_from=0), "mlp": None},
+        {"type": "latent_attention", "mixer": _latent(4, 16, 16, 24, 40, 56, 0.18, 23, 16, base=2e5), "mlp": _moe(6, 2, 32)},
+        {"type": "attention", "mixer": _attention(4, 2, 24, 0.2, (0.4, 16)), "mlp": _moe(9, 1, 48)},
+        {"type": "latent_attention", "mixer": _latent(2, 32, 16, 48, 24, 56, 0.15, 61, 16, base=2e5, kv_from=0), "mlp": None},
         {"type": "attention", "mixer": _attention(6, 6, 16, 0.25), "mlp": _moe(4, 4, 24)},
         {"type": "latent_attention", "mixer": _latent(3, 24, 8, 16, 48, 32, 0.2, 40, 4), "mlp": _moe(5, 2, 40)},
         {"type": "latent_attention", "mixer": _latent(5, 8, 8, 32, 16, 32, 0.3, 9, 4, kv_from=4), "mlp": _moe(6, 2, 32)},
@@ -65,10 +65,10 @@ ALL_KINDS = {
 # widths and expert sizes in 64s
 TENSOR_CORE_SIZES = {
     "architecture": "Zeridra", "vocab": 384, "width": 192, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.5},
-    "logit_scale": 0.25, "logit_softcap": 30.0,
+    "logit_scale": 0.4, "logit_softcap": 20.0,
     "layers": [
         {"type": "latent_attention", "mixer": _latent(4, 32, 32, 64, 64, 96, 0.125, 70, 32, base=1e5), "mlp": _moe(8, 2, 128)},
-        {"type": "attention", "mixer": _attention(4, 2, 64, 0.125, (0.3, 32)), "mlp": _moe(6, 1, 64)},
+        {"type": "attention", "mixer": _attention(4, 2, 64, 0.125, (0.25, 32)), "mlp": _moe(6, 1, 64)},
         {"type": "latent_attention", "mixer": _latent(8, 64, 16, 32, 128, 48, 0.1, 150, 16), "mlp": None},
         {"type": "attention", "mixer": _attention(2, 1, 128, 0.09), "mlp": _moe(4, 3, 128)},
         {"type": "latent_attention", "mixer": _latent(2, 64, 32, 128, 64, 96, 0.1, 33, 32, base=1e5, kv_from=0), "mlp": _moe(8, 8, 64)},
